@@ -151,6 +151,24 @@ int l3_generate_ragged(L3Model* m, const int32_t* ids, const int32_t* lens, int 
 #define L3_MIX_MINGRU 4        /* element-wise gated recurrence of width dim (heads = vdim = 1):
                                   S <- (1 - z) S + z c,  z = sigmoid(Wz h + bz),  c = u + 1/2 (u >= 0) | sigmoid(u),
                                   u = Wx h + bx;  output Wo (S * silu(Wg h))                                            */
+#define L3_MIX_DIFF 5          /* differential sliding-window attention: every query / key head holds two maps of size dim
+                                  ([map 1 | map 2]) that attend over the same values (GQA, value size vdim) and are combined
+                                  as a1 - lambda a2, lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff, followed by an RMS
+                                  norm without weight over the head's values times (1 - diff); q / k / v have biases;
+                                  q and k get an RMS norm per head and map (one weight vector of size dim each) and then
+                                  rotary positions on the first rot_dims entries of each map, entry i paired with entry
+                                  i + rot_dims / 2, frequencies rot_base^(-2 i / rot_dims) rescaled by wavelength
+                                  (rot_scale_*); query i sees keys j with 0 <= i - j < window (window 0: every earlier key).
+                                  Built for parallel layers (L3StackConfig::parallel)                                     */
+/* feed-forward kinds (L3LayerSpec::ff_kind) */
+#define L3_FF_GLU 0            /* down(act(gate x) * (up x)), act = L3StackConfig::glu_act; experts: down relu(up x)^2 */
+#define L3_FF_POLYNORM 1       /* down(P(up x)),  P(z) = a N(z) + b N(z^2) + c N(z^3) + e with element-wise powers and
+                                  N(v) = v / sqrt(mean(v^2) + eps) over the ff values of a token; tensor l<i>.mlp.act = (a, b, c, e) */
+/* router kinds (L3LayerSpec::router_kind) */
+#define L3_ROUTE_SOFTMAX 0     /* softmax scores, correction, groups, identity slots; the weight multiplies the expert's output */
+#define L3_ROUTE_SIGMOID_IN 1  /* scores = sigmoid(logits); the `top` largest are chosen (ties: lower slot), their weights are
+                                  the scores themselves; the weight multiplies the expert's INPUT; experts are gated units
+                                  down(silu(gate x) * (up x)); a shared expert of width shared_ff (0: none) runs for every token */
 typedef struct L3LayerSpec {
   int32_t mixer;        /* L3_MIX_* */
   int32_t heads;        /* value heads (query heads for L3_MIX_SOFTMAX) */
@@ -173,6 +191,17 @@ typedef struct L3LayerSpec {
    * ones by router_scale * score (not renormalised); an identity slot returns its input */
   int32_t experts, top, identity, groups, groups_keep;
   float router_scale;
+  /* L3_MIX_DIFF (also uses heads, kv_heads, dim, vdim, scale, rot_dims, rot_base) */
+  int32_t window;            /* keys a query sees, itself included; 0 = all */
+  float diff;                /* constant of lambda and of the output multiplier (1 - diff) */
+  /* wavelength-dependent rescaling of the rotary frequencies (rot_scale_original 0: none): with l = 2 pi / f, f stays
+   * where l < original / high, becomes f / factor where l > original / low, and in between
+   * (1 - s) f / factor + s f with s = (original / l - low) / (high - low) */
+  float rot_scale_factor, rot_scale_low, rot_scale_high;
+  int32_t rot_scale_original;
+  int32_t ff_kind;           /* L3_FF_* of the dense feed-forward */
+  int32_t router_kind;       /* L3_ROUTE_* of the mixture of experts */
+  int32_t shared_ff;         /* L3_ROUTE_SIGMOID_IN: width of the shared expert; 0 = none */
 } L3LayerSpec;
 
 typedef struct L3StackConfig {
@@ -193,6 +222,16 @@ typedef struct L3StackConfig {
    * caches and states; ahead of pass t the row t of the tensor "loop.step" [loop_times, width] is added to x.
    * loop_times 0 = no loop.  A "layer run" is one execution of a layer; runs are numbered in execution order. */
   int32_t loop_start, loop_stop, loop_times;
+  /* parallel layers (needs norm_input): ONE norm per layer, h = norm1(x), and both sublayers read it:
+   *   X_(i+1) = x + ls1 * mixer(h + conv1(h)) + ls2 * ff(h + conv2(h))
+   * norm_center 1: the norms (layer norms and the final norm) subtract the mean first (layer norm with a weight, no bias);
+   * layer_scale 1: tensors l<i>.ls1 / ls2 [width] multiply the sublayers' results (0: ones);
+   * canon_taps T > 0: every sublayer reads h + conv(h), conv(h)_t = sum_j w[:, j] h_(t - T + 1 + j), a causal convolution
+   *   over time per channel (tensors l<i>.canon1 / canon2 [width, T], zeros ahead of position 0; the last T - 1 rows of h
+   *   are kept per sequence slot and layer run);
+   * depth_avg 1: what goes on to the next layer (and to the final norm) is sum_(j <= i+1) dwa_i[j] X_j with X_0 the
+   *   embedding output and X_(i+1) layer i's own result (tensor l<i>.dwa [i + 2]). */
+  int32_t parallel, norm_center, layer_scale, canon_taps, depth_avg;
 } L3StackConfig;
 
 int l3_create_stack(const L3StackConfig* cfg, const L3LayerSpec* layers, L3Model** out);

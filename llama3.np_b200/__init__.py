@@ -22,6 +22,9 @@ def __getattr__(name):  # lazy: importing the package must not require the built
     if name == "Rakelorn":
         from .rakelorn import Rakelorn
         return Rakelorn
+    if name == "Mabedra":
+        from .mabedra import Mabedra
+        return Mabedra
     if name in ("StackDecoder", "StackConfig", "LayerSpec"):
         from . import stack as _s
         return getattr(_s, name)

@@ -24,7 +24,9 @@ class L3Config(C.Structure):
                 ("tp_world", C.c_int32), ("flags", C.c_int32)]
 
 
-MIX_SOFTMAX, MIX_DECAY_LINEAR, MIX_GATED_DELTA, MIX_LATENT, MIX_MINGRU = 0, 1, 2, 3, 4
+MIX_SOFTMAX, MIX_DECAY_LINEAR, MIX_GATED_DELTA, MIX_LATENT, MIX_MINGRU, MIX_DIFF = 0, 1, 2, 3, 4, 5
+FF_GLU, FF_POLYNORM = 0, 1
+ROUTE_SOFTMAX, ROUTE_SIGMOID_IN = 0, 1
 GLU_SILU, GLU_GELU_TANH = 0, 1
 
 
@@ -35,7 +37,10 @@ class L3LayerSpec(C.Structure):
                 ("q_rank", C.c_int32), ("kv_rank", C.c_int32), ("rot_dim", C.c_int32), ("rot_dims", C.c_int32),
                 ("rot_base", C.c_double),
                 ("experts", C.c_int32), ("top", C.c_int32), ("identity", C.c_int32), ("groups", C.c_int32),
-                ("groups_keep", C.c_int32), ("router_scale", C.c_float)]
+                ("groups_keep", C.c_int32), ("router_scale", C.c_float),
+                ("window", C.c_int32), ("diff", C.c_float), ("rot_scale_factor", C.c_float), ("rot_scale_low", C.c_float),
+                ("rot_scale_high", C.c_float), ("rot_scale_original", C.c_int32), ("ff_kind", C.c_int32),
+                ("router_kind", C.c_int32), ("shared_ff", C.c_int32)]
 
 
 class L3StackConfig(C.Structure):
@@ -44,7 +49,9 @@ class L3StackConfig(C.Structure):
                 ("norm_eps", C.c_float), ("residual_mult", C.c_float), ("norm_one_plus", C.c_int32),
                 ("glu_act", C.c_int32), ("side_dim", C.c_int32),
                 ("norm_input", C.c_int32), ("norm_scalar", C.c_int32), ("token_shift", C.c_int32),
-                ("embed_scale", C.c_float), ("loop_start", C.c_int32), ("loop_stop", C.c_int32), ("loop_times", C.c_int32)]
+                ("embed_scale", C.c_float), ("loop_start", C.c_int32), ("loop_stop", C.c_int32), ("loop_times", C.c_int32),
+                ("parallel", C.c_int32), ("norm_center", C.c_int32), ("layer_scale", C.c_int32), ("canon_taps", C.c_int32),
+                ("depth_avg", C.c_int32)]
 
 
 _P = C.c_void_p

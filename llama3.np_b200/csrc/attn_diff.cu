@@ -1,0 +1,455 @@
+// Differential sliding-window attention (L3_MIX_DIFF, include/llama3_b200.h).
+//
+// Every query head holds two maps [map 1 | map 2] of size DK; key head g likewise; both maps of a query head attend over
+// the SAME values (size DV) of its key head with a softmax of their own, and the head's output is
+//     o = a1 - lambda a2,   o <- o / sqrt(mean(o^2) + eps) * (1 - diff).
+// Query i sees keys j with 0 <= i - j < window.  Scores, softmax weights, sums and the norm are fp32 in both modes.
+//
+//  * diff_lambda_kernel      lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff, once per layer at finalize
+//  * diff_prep_kernel        bias, RMS norm per head and map (one weight vector), rotary turn of the first rot_dims entries of
+//                            each map (entry i with entry i + rot_dims / 2) at angle position * f_i in fp32, append of the keys
+//                            [maxB, 2 G, M, DK] (head g, map m at 2 g + m) and of the biased values [maxB, G, M, DV]
+//  * attn_diff_tile_kernel   prompts: 64 queries x 64 keys per tile for one head, both maps at once - two score tiles, two
+//                            online softmaxes, two accumulators fed by the same value rows; tiles outside the window are
+//                            never visited; the combination and the head norm are the epilogue
+//  * attn_diff_cta_kernel    decode, short portions and head sizes outside the tiled list: a CTA per (token, head), its warps
+//                            split the visible keys (a lane scores one key for both maps), merged through shared memory
+#include <algorithm>
+
+#include "common.cuh"
+#include "mixer.h"
+
+namespace {
+
+__global__ void diff_lambda_kernel(const float* __restrict__ v, int n, float diff, float* __restrict__ out) {
+  // v = lq1 | lk1 | lq2 | lk2, n entries each; one warp
+  const int lane = threadIdx.x;
+  float s1 = 0.f, s2 = 0.f;
+  for (int i = lane; i < n; i += 32) { s1 = fmaf(v[i], v[n + i], s1); s2 = fmaf(v[2 * n + i], v[3 * n + i], s2); }
+  s1 = warp_sum(s1);
+  s2 = warp_sum(s2);
+  if (lane == 0) *out = expf(s1) - expf(s2) + diff;
+}
+
+template <typename KVT>
+__global__ void __launch_bounds__(256) diff_prep_kernel(DiffPrepArgs a) {
+  extern __shared__ float sm[];  // per warp: one map's normed vector [DK]
+  pdl_launch();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const size_t r = blockIdx.x;
+  const int b = (int)(r / a.L), t = (int)(r - (size_t)b * a.L);
+  const int pos = *a.pos_ptr + t;
+  const int DK = a.DK, half = a.rot_dims >> 1;
+  const float* pr = a.proj + r * a.ld;
+  float* vbuf = sm + (size_t)warp * DK;
+  const int nq = 2 * a.H, nk = 2 * a.G;
+  for (int vec = warp; vec < nq + nk; vec += nw) {
+    const bool isq = vec < nq;
+    const int col = isq ? a.q_off + vec * DK : a.k_off + (vec - nq) * DK;
+    const float* w = isq ? a.wq : a.wk;
+    float ss = 0.f;
+    for (int d = lane; d < DK; d += 32) {
+      const float v = pr[col + d] + a.bias[col + d];
+      vbuf[d] = v;
+      ss = fmaf(v, v, ss);
+    }
+    const float rinv = 1.0f / sqrtf(warp_sum(ss) / (float)DK + a.eps);
+    __syncwarp();
+    for (int d = lane; d < DK; d += 32) vbuf[d] = vbuf[d] * rinv * w[d];
+    __syncwarp();
+    KVT* kdst = isq ? nullptr : (KVT*)a.cache_k + (((size_t)b * nk + (vec - nq)) * a.M + pos) * DK;
+    float* qdst = isq ? a.q_out + r * ((size_t)nq * DK) + (size_t)vec * DK : nullptr;
+    for (int d = lane; d < DK; d += 32) {
+      float o = vbuf[d];
+      if (d < a.rot_dims) {
+        const int i = d < half ? d : d - half;
+        float sn, cs;
+        sincosf((float)pos * a.inv_freq[i], &sn, &cs);
+        o = d < half ? vbuf[d] * cs - vbuf[d + half] * sn : vbuf[d] * cs + vbuf[d - half] * sn;
+      }
+      if (isq) qdst[d] = o;
+      else kdst[d] = from_f32<KVT>(o);
+    }
+    __syncwarp();
+  }
+  const int nv = a.G * a.DV;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const int g = i / a.DV, d = i - g * a.DV;
+    ((KVT*)a.cache_v)[(((size_t)b * a.G + g) * a.M + pos) * a.DV + d] = from_f32<KVT>(pr[a.v_off + i] + a.bias[a.v_off + i]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- generic CTA kernel
+template <typename KVT>
+__device__ __forceinline__ float dot_row(const float* __restrict__ q, const KVT* __restrict__ k, int n) {
+  constexpr int VEC = Vec16<KVT>::N;
+  float acc = 0.f;
+  if (n % VEC == 0) {
+    for (int d = 0; d < n; d += VEC) {
+      float f[VEC];
+      Vec16<KVT>::unpack(*reinterpret_cast<const uint4*>(k + d), f);
+#pragma unroll
+      for (int x = 0; x < VEC; ++x) acc = fmaf(q[d + x], f[x], acc);
+    }
+  } else {
+    for (int d = 0; d < n; ++d) acc = fmaf(q[d], to_f32(k[d]), acc);
+  }
+  return acc;
+}
+
+constexpr int DIFF_CTA_WARPS = 8;
+
+template <typename KVT>
+__global__ void __launch_bounds__(DIFF_CTA_WARPS * 32) attn_diff_cta_kernel(DiffAttnArgs a) {
+  extern __shared__ __align__(16) float sm[];
+  constexpr int NW = DIFF_CTA_WARPS;
+  const int DK = a.DK, DV = a.DV;
+  float* qs = sm;                       // [2][DK]
+  float* os = qs + 2 * DK;              // [NW][2][DV]
+  float* st = os + (size_t)NW * 2 * DV; // [NW][4]: m1, l1, m2, l2
+  float* red = st + NW * 4;             // [32]
+  pdl_launch();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int head = blockIdx.x % a.H;
+  const size_t row = blockIdx.x / a.H;
+  const int b = (int)(row / a.L), t = (int)(row - (size_t)b * a.L);
+  const int last = *a.pos_ptr + t;
+  const int lo = a.window > 0 ? max(0, last - a.window + 1) : 0;
+  const int g = head / (a.H / a.G);
+  for (int d = threadIdx.x; d < 2 * DK; d += blockDim.x) qs[d] = a.q[(row * a.H + head) * (size_t)(2 * DK) + d];
+  float* o1 = os + (size_t)warp * 2 * DV;
+  float* o2 = o1 + DV;
+  for (int d = lane; d < 2 * DV; d += 32) o1[d] = 0.f;
+  __syncthreads();
+  const KVT* k1 = (const KVT*)a.cache_k + ((size_t)b * 2 * a.G + 2 * g) * a.M * DK;
+  const KVT* k2 = k1 + (size_t)a.M * DK;
+  const KVT* vb = (const KVT*)a.cache_v + ((size_t)b * a.G + g) * a.M * DV;
+  float m1 = -INFINITY, l1 = 0.f, m2 = -INFINITY, l2 = 0.f;
+  for (int j0 = lo + warp * 32; j0 <= last; j0 += NW * 32) {
+    const int j = j0 + lane;
+    float s1 = -INFINITY, s2 = -INFINITY;
+    if (j <= last) {
+      s1 = dot_row<KVT>(qs, k1 + (size_t)j * DK, DK) * a.scale;
+      s2 = dot_row<KVT>(qs + DK, k2 + (size_t)j * DK, DK) * a.scale;
+    }
+    const float n1 = fmaxf(m1, warp_max(s1)), n2 = fmaxf(m2, warp_max(s2));
+    const float p1 = j <= last ? expf(s1 - n1) : 0.f, p2 = j <= last ? expf(s2 - n2) : 0.f;
+    const float al1 = expf(m1 - n1), al2 = expf(m2 - n2);  // first batch: exp(-inf) = 0 and o, l are 0
+    l1 = l1 * al1 + warp_sum(p1);
+    l2 = l2 * al2 + warp_sum(p2);
+    m1 = n1; m2 = n2;
+    const int nb = min(32, last + 1 - j0);
+    for (int d0 = 0; d0 < DV; d0 += 32) {  // every lane runs every round: the shuffles name the full warp
+      const int d = d0 + lane;
+      const bool ok = d < DV;
+      float c1 = ok ? o1[d] * al1 : 0.f, c2 = ok ? o2[d] * al2 : 0.f;
+      for (int u = 0; u < nb; ++u) {
+        const float pu1 = __shfl_sync(L3_FULL, p1, u), pu2 = __shfl_sync(L3_FULL, p2, u);
+        if (ok) {
+          const float v = to_f32(vb[(size_t)(j0 + u) * DV + d]);
+          c1 = fmaf(pu1, v, c1);
+          c2 = fmaf(pu2, v, c2);
+        }
+      }
+      if (ok) { o1[d] = c1; o2[d] = c2; }
+    }
+  }
+  if (lane == 0) { st[warp * 4] = m1; st[warp * 4 + 1] = l1; st[warp * 4 + 2] = m2; st[warp * 4 + 3] = l2; }
+  __syncthreads();
+  // merge the warps' partial softmaxes (a warp without keys has m = -inf, l = 0 and weighs nothing)
+  float M1 = -INFINITY, M2 = -INFINITY;
+  for (int w = 0; w < NW; ++w) { M1 = fmaxf(M1, st[w * 4]); M2 = fmaxf(M2, st[w * 4 + 2]); }
+  float L1 = 0.f, L2 = 0.f;
+  for (int w = 0; w < NW; ++w) { L1 += st[w * 4 + 1] * expf(st[w * 4] - M1); L2 += st[w * 4 + 3] * expf(st[w * 4 + 2] - M2); }
+  const float lam = *a.lambda;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < DV; d += blockDim.x) {
+    float c1 = 0.f, c2 = 0.f;
+    for (int w = 0; w < NW; ++w) {
+      c1 = fmaf(os[((size_t)w * 2) * DV + d], expf(st[w * 4] - M1), c1);
+      c2 = fmaf(os[((size_t)w * 2 + 1) * DV + d], expf(st[w * 4 + 2] - M2), c2);
+    }
+    const float o = c1 / L1 - lam * (c2 / L2);
+    os[d] = o;                     // warp 0's map-1 slot: every d is written by exactly one thread after its reads
+    ss = fmaf(o, o, ss);
+  }
+  // block sum of ss
+  ss = warp_sum(ss);
+  __syncthreads();
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < NW; ++w) tot += red[w];
+  const float mul = (1.0f - a.diff) / sqrtf(tot / (float)DV + a.eps);
+  for (int d = threadIdx.x; d < DV; d += blockDim.x) {
+    const float v = os[d] * mul;
+    const size_t oi = (row * a.H + head) * (size_t)DV + d;
+    a.out[oi] = v;
+    if (a.out16) a.out16[oi] = __float2bfloat16_rn(v);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- tiled prompt kernel
+template <typename KVT> __device__ __forceinline__ float4 ld_kv4(const KVT* p);
+template <> __device__ __forceinline__ float4 ld_kv4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 ld_kv4<bf16>(const bf16* p) {
+  const uint2 r = *reinterpret_cast<const uint2*>(p);
+  return make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xffff0000u), __uint_as_float(r.y << 16),
+                     __uint_as_float(r.y & 0xffff0000u));
+}
+
+constexpr int DT_ROWS = 64, DT_TK = 64, DT_LDS = DT_TK + 4;
+
+template <int DK, int DV>
+constexpr size_t diff_tile_smem() {
+  return (size_t)(2 * DT_ROWS * (DK + 4) + 2 * DT_TK * (DK + 4) + DT_TK * DV + 2 * DT_ROWS * DT_LDS + 6 * DT_ROWS) * sizeof(float);
+}
+
+template <int DK, int DV, typename KVT>
+__global__ void __launch_bounds__(256) attn_diff_tile_kernel(DiffAttnArgs a) {
+  constexpr int LDK = DK + 4, DK4 = DK / 4, DV4 = DV / 4, NCH = (DV + 63) / 64;
+  extern __shared__ __align__(16) float sm[];
+  float* Qs = sm;                           // [2][ROWS][LDK]
+  float* Ks = Qs + 2 * DT_ROWS * LDK;       // [2][TK][LDK]
+  float* Vs = Ks + 2 * DT_TK * LDK;         // [TK][DV]
+  float* Ss = Vs + DT_TK * DV;              // [2][ROWS][LDS]
+  float* St = Ss + 2 * DT_ROWS * DT_LDS;    // [2][ROWS][3]: running max, running sum, rescale of this tile
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int ty = tid >> 4, tx = tid & 15;
+  const int head = blockIdx.y, b = blockIdx.z;
+  const int g = head / (a.H / a.G);
+  pdl_launch();
+  pdl_wait();
+  const int start = *a.pos_ptr;
+  const int q0 = (gridDim.x - 1 - blockIdx.x) * DT_ROWS;  // long tiles first
+  const int nq = min(DT_ROWS, a.L - q0);
+  const int t_hi = start + q0 + nq;  // one past the last visible key
+  const int k_lo = a.window > 0 ? max(0, start + q0 - a.window + 1) : 0;
+  for (int i = tid; i < 2 * DT_ROWS * DK4; i += 256) {
+    const int mp = i / (DT_ROWS * DK4), rem = i - mp * (DT_ROWS * DK4);
+    const int r = rem / DK4, d4 = rem - r * DK4;
+    float4 v = make_float4(0, 0, 0, 0);
+    if (r < nq) v = *reinterpret_cast<const float4*>(a.q + (((size_t)b * a.L + q0 + r) * a.H + head) * (2 * DK) + mp * DK + d4 * 4);
+    *reinterpret_cast<float4*>(Qs + (mp * DT_ROWS + r) * LDK + d4 * 4) = v;
+  }
+  for (int i = tid; i < 2 * DT_ROWS; i += 256) { St[i * 3] = -INFINITY; St[i * 3 + 1] = 0.f; St[i * 3 + 2] = 1.f; }
+  float4 acc[2][4][NCH];
+#pragma unroll
+  for (int mp = 0; mp < 2; ++mp)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) acc[mp][i][c] = make_float4(0, 0, 0, 0);
+  const KVT* kbase = (const KVT*)a.cache_k + ((size_t)b * 2 * a.G + 2 * g) * a.M * DK;
+  const KVT* vbase = (const KVT*)a.cache_v + ((size_t)b * a.G + g) * a.M * DV;
+
+  for (int k0 = k_lo; k0 < t_hi; k0 += DT_TK) {
+    __syncthreads();
+    for (int i = tid; i < 2 * DT_TK * DK4; i += 256) {
+      const int mp = i / (DT_TK * DK4), rem = i - mp * (DT_TK * DK4);
+      const int key = rem / DK4, d4 = rem - key * DK4;
+      const int t = k0 + key;
+      float4 kv = make_float4(0, 0, 0, 0);
+      if (t < t_hi) kv = ld_kv4<KVT>(kbase + ((size_t)mp * a.M + t) * DK + d4 * 4);
+      *reinterpret_cast<float4*>(Ks + (mp * DT_TK + key) * LDK + d4 * 4) = kv;
+    }
+    for (int i = tid; i < DT_TK * DV4; i += 256) {
+      const int key = i / DV4, d4 = i - key * DV4;
+      const int t = k0 + key;
+      float4 vv = make_float4(0, 0, 0, 0);
+      if (t < t_hi) vv = ld_kv4<KVT>(vbase + (size_t)t * DV + d4 * 4);
+      *reinterpret_cast<float4*>(Vs + key * DV + d4 * 4) = vv;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int mp = 0; mp < 2; ++mp) {  // scores of both maps: queries ty * 4 + i, keys tx + 16 j
+      float s[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+      const float* Qm = Qs + mp * DT_ROWS * LDK;
+      const float* Km = Ks + mp * DT_TK * LDK;
+#pragma unroll 2
+      for (int d4 = 0; d4 < DK4; ++d4) {
+        float4 qv[4], kv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) qv[i] = *reinterpret_cast<const float4*>(Qm + (ty * 4 + i) * LDK + d4 * 4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) kv[j] = *reinterpret_cast<const float4*>(Km + (tx + 16 * j) * LDK + d4 * 4);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            s[i][j] = fmaf(qv[i].x, kv[j].x, s[i][j]); s[i][j] = fmaf(qv[i].y, kv[j].y, s[i][j]);
+            s[i][j] = fmaf(qv[i].z, kv[j].z, s[i][j]); s[i][j] = fmaf(qv[i].w, kv[j].w, s[i][j]);
+          }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = ty * 4 + i;
+        const int qpos = start + q0 + r;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int key = tx + 16 * j, kp = k0 + key;
+          const bool vis = r < nq && kp <= qpos && (a.window <= 0 || qpos - kp < a.window);
+          Ss[(mp * DT_ROWS + r) * DT_LDS + key] = vis ? s[i][j] * a.scale : -INFINITY;
+        }
+      }
+    }
+    __syncthreads();
+    for (int rr = 0; rr < 16; ++rr) {  // online softmax: warp w owns rows 16 w .. 16 w + 15 of the 128 (map, query) rows
+      const int r = warp * 16 + rr;
+      float* srow = Ss + r * DT_LDS;
+      const float mold = St[r * 3];
+      const float s0 = srow[lane], s1 = srow[lane + 32];
+      const float mnew = fmaxf(mold, warp_max(fmaxf(s0, s1)));
+      float p0 = 0.f, p1 = 0.f, alpha = 1.f;
+      if (mnew > -INFINITY) {
+        p0 = expf(s0 - mnew);
+        p1 = expf(s1 - mnew);
+        alpha = expf(mold - mnew);
+      }
+      const float ps = warp_sum(p0 + p1);
+      srow[lane] = p0;
+      srow[lane + 32] = p1;
+      if (lane == 0) { St[r * 3 + 1] = St[r * 3 + 1] * alpha + ps; St[r * 3] = mnew; St[r * 3 + 2] = alpha; }
+    }
+    __syncthreads();
+    {  // o_m = o_m * alpha_m + P_m V for both maps; a value row read once feeds both
+#pragma unroll
+      for (int mp = 0; mp < 2; ++mp)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float alpha = St[(mp * DT_ROWS + ty * 4 + i) * 3 + 2];
+#pragma unroll
+          for (int c = 0; c < NCH; ++c) { acc[mp][i][c].x *= alpha; acc[mp][i][c].y *= alpha; acc[mp][i][c].z *= alpha; acc[mp][i][c].w *= alpha; }
+        }
+#pragma unroll 2
+      for (int k4 = 0; k4 < DT_TK / 4; ++k4) {
+        float4 p[2][4];
+#pragma unroll
+        for (int mp = 0; mp < 2; ++mp)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) p[mp][i] = *reinterpret_cast<const float4*>(Ss + (mp * DT_ROWS + ty * 4 + i) * DT_LDS + k4 * 4);
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          const int d = tx * 4 + 64 * c;
+          if (d < DV) {
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              const float4 v = *reinterpret_cast<const float4*>(Vs + (k4 * 4 + kk) * DV + d);
+#pragma unroll
+              for (int mp = 0; mp < 2; ++mp)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float pw = kk == 0 ? p[mp][i].x : kk == 1 ? p[mp][i].y : kk == 2 ? p[mp][i].z : p[mp][i].w;
+                  acc[mp][i][c].x = fmaf(pw, v.x, acc[mp][i][c].x); acc[mp][i][c].y = fmaf(pw, v.y, acc[mp][i][c].y);
+                  acc[mp][i][c].z = fmaf(pw, v.z, acc[mp][i][c].z); acc[mp][i][c].w = fmaf(pw, v.w, acc[mp][i][c].w);
+                }
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const float lam = *a.lambda;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = ty * 4 + i;
+    const float i1 = 1.0f / St[r * 3 + 1], i2 = lam / St[(DT_ROWS + r) * 3 + 1];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      float4& o = acc[0][i][c];
+      const float4 o2 = acc[1][i][c];
+      o.x = o.x * i1 - o2.x * i2; o.y = o.y * i1 - o2.y * i2; o.z = o.z * i1 - o2.z * i2; o.w = o.w * i1 - o2.w * i2;
+      if (tx * 4 + 64 * c < DV) ss += o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w;
+    }
+    // the 16 threads of a query row are 16 adjacent lanes
+#pragma unroll
+    for (int off = 8; off > 0; off >>= 1) ss += __shfl_xor_sync(L3_FULL, ss, off);
+    const float mul = (1.0f - a.diff) / sqrtf(ss / (float)DV + a.eps);
+    if (r >= nq) continue;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int d = tx * 4 + 64 * c;
+      if (d >= DV) continue;
+      float4 o = acc[0][i][c];
+      o.x *= mul; o.y *= mul; o.z *= mul; o.w *= mul;
+      const size_t oi = (((size_t)b * a.L + q0 + r) * a.H + head) * DV + d;
+      *reinterpret_cast<float4*>(a.out + oi) = o;
+      if (a.out16) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(o.x, o.y), hi = __floats2bfloat162_rn(o.z, o.w);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&lo);
+        pk.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(a.out16 + oi) = pk;
+      }
+    }
+  }
+}
+
+template <int DK, int DV, typename KVT>
+cudaError_t launch_tile(const DiffAttnArgs& a, cudaStream_t s) {
+  auto kern = attn_diff_tile_kernel<DK, DV, KVT>;
+  constexpr size_t smem = diff_tile_smem<DK, DV>();
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  return launch_k(kern, dim3((a.L + DT_ROWS - 1) / DT_ROWS, a.H, a.B), dim3(256), smem, s, a);
+}
+
+template <typename KVT>
+cudaError_t launch_tile_t(const DiffAttnArgs& a, cudaStream_t s) {
+  if (a.DK == 32 && a.DV == 32) return launch_tile<32, 32, KVT>(a, s);
+  if (a.DK == 32 && a.DV == 64) return launch_tile<32, 64, KVT>(a, s);
+  if (a.DK == 64 && a.DV == 64) return launch_tile<64, 64, KVT>(a, s);
+  if (a.DK == 64 && a.DV == 128) return launch_tile<64, 128, KVT>(a, s);
+  if (a.DK == 128 && a.DV == 128) return launch_tile<128, 128, KVT>(a, s);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+cudaError_t launch_diff_lambda(const float* vecs, int n, float diff, float* out, cudaStream_t s) {
+  diff_lambda_kernel<<<1, 32, 0, s>>>(vecs, n, diff, out);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_diff_prep(const DiffPrepArgs& a, int rows, bool kv_bf16, cudaStream_t s) {
+  const int nvec = 2 * (a.H + a.G);
+  const int warps = std::max(2, std::min(8, nvec));
+  const size_t smem = (size_t)warps * a.DK * sizeof(float);
+  if (smem > 48 * 1024) return cudaErrorInvalidValue;
+  if (kv_bf16) return launch_k(diff_prep_kernel<bf16>, dim3(rows), dim3(warps * 32), smem, s, a);
+  return launch_k(diff_prep_kernel<float>, dim3(rows), dim3(warps * 32), smem, s, a);
+}
+
+bool diff_attn_tiled(int DK, int DV) {
+  return (DK == 32 && (DV == 32 || DV == 64)) || (DK == 64 && (DV == 64 || DV == 128)) || (DK == 128 && DV == 128);
+}
+
+size_t diff_attn_cta_smem(int DK, int DV) {
+  return (size_t)(2 * DK + DIFF_CTA_WARPS * 2 * DV + DIFF_CTA_WARPS * 4 + 32) * sizeof(float);
+}
+
+bool diff_attn_supported(int DK, int DV) { return diff_attn_cta_smem(DK, DV) <= 200 * 1024 && DK <= 12 * 1024 / 4; }
+
+cudaError_t launch_diff_attn(const DiffAttnArgs& a, bool kv_bf16, cudaStream_t s) {
+  static const int tile_min = [] { const char* v = getenv("L3_DIFF_TILE_MIN"); return v ? atoi(v) : 16; }();
+  if (tile_min > 0 && a.L >= tile_min && diff_attn_tiled(a.DK, a.DV))
+    return kv_bf16 ? launch_tile_t<bf16>(a, s) : launch_tile_t<float>(a, s);
+  const size_t smem = diff_attn_cta_smem(a.DK, a.DV);
+  const dim3 grid((unsigned)((size_t)a.B * a.L * a.H));
+  if (kv_bf16) {
+    auto kern = attn_diff_cta_kernel<bf16>;
+    if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; }
+    return launch_k(kern, grid, dim3(DIFF_CTA_WARPS * 32), smem, s, a);
+  }
+  auto kern = attn_diff_cta_kernel<float>;
+  if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; }
+  return launch_k(kern, grid, dim3(DIFF_CTA_WARPS * 32), smem, s, a);
+}

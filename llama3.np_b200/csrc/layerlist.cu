@@ -49,13 +49,18 @@ static int pad8(int v) { return (v + 7) & ~7; }
 
 // ------------------------------------------------------------------------------ create
 static int check_spec(const L3StackConfig* c, const L3LayerSpec& s, int i) {
-  REQUIRE(nullptr, s.mixer >= L3_MIX_SOFTMAX && s.mixer <= L3_MIX_MINGRU, "layer %d: unknown mixer %d", i, s.mixer);
+  REQUIRE(nullptr, s.mixer >= L3_MIX_SOFTMAX && s.mixer <= L3_MIX_DIFF, "layer %d: unknown mixer %d", i, s.mixer);
+  REQUIRE(nullptr, (s.mixer == L3_MIX_DIFF) == (c->parallel != 0), "layer %d: differential attention and parallel layers come together", i);
+  REQUIRE(nullptr, s.ff_kind == L3_FF_GLU || (s.ff_kind == L3_FF_POLYNORM && c->parallel), "layer %d: this feed-forward kind is built for parallel layers", i);
+  REQUIRE(nullptr, s.router_kind == L3_ROUTE_SOFTMAX || (s.router_kind == L3_ROUTE_SIGMOID_IN && c->parallel), "layer %d: this router kind is built for parallel layers", i);
+  REQUIRE(nullptr, !(c->parallel && s.experts > 0) || s.router_kind == L3_ROUTE_SIGMOID_IN, "layer %d: parallel layers take the sigmoid router", i);
   REQUIRE(nullptr, s.heads >= 1 && s.dim >= 1 && s.vdim >= 1 && s.ff >= 0, "layer %d: bad sizes", i);
   REQUIRE(nullptr, s.mixer <= L3_MIX_GATED_DELTA || c->norm_input, "layer %d: this mixer is built for pre-norm layers (norm_input)", i);
   if (s.experts > 0) {
     const int n = s.experts + s.identity;
     REQUIRE(nullptr, c->norm_input, "layer %d: the mixture of experts is built for pre-norm layers (norm_input)", i);
     REQUIRE(nullptr, s.ff >= 1 && s.identity >= 0 && s.top >= 1 && s.top <= n && n <= 1024, "layer %d: bad expert counts", i);
+    REQUIRE(nullptr, s.router_kind == L3_ROUTE_SOFTMAX || (s.identity == 0 && s.top <= s.experts && s.shared_ff >= 0), "layer %d: bad sigmoid-router sizes", i);
     REQUIRE(nullptr, s.groups >= 1 && n % s.groups == 0 && s.groups_keep >= 1 && s.groups_keep <= s.groups, "layer %d: bad expert groups", i);
   }
   if (s.mixer == L3_MIX_LATENT) {
@@ -63,6 +68,12 @@ static int check_spec(const L3StackConfig* c, const L3LayerSpec& s, int i) {
             "layer %d: bad latent / rotary sizes", i);
     REQUIRE(nullptr, s.rot_dims == 0 || s.rot_base > 0, "layer %d: rotary base must be positive", i);
     REQUIRE(nullptr, latent_attn_supported(s.kv_rank + s.rot_dim, s.kv_rank), "layer %d: latent row of %d + %d entries unsupported", i, s.kv_rank, s.rot_dim);
+  } else if (s.mixer == L3_MIX_DIFF) {
+    REQUIRE(nullptr, s.kv_heads >= 1 && s.heads % s.kv_heads == 0, "layer %d: heads %% kv_heads != 0", i);
+    REQUIRE(nullptr, s.rot_dims >= 0 && s.rot_dims <= s.dim && s.rot_dims % 2 == 0 && (s.rot_dims == 0 || s.rot_base > 0), "layer %d: bad rotary sizes", i);
+    REQUIRE(nullptr, s.rot_scale_original == 0 || (s.rot_scale_factor > 0 && s.rot_scale_high != s.rot_scale_low && s.rot_scale_low > 0 && s.rot_scale_high > 0),
+            "layer %d: bad rotary scaling", i);
+    REQUIRE(nullptr, s.window >= 0 && diff_attn_supported(s.dim, s.vdim), "layer %d: window %d / head sizes %d, %d unsupported", i, s.window, s.dim, s.vdim);
   } else if (s.mixer == L3_MIX_MINGRU) {
     REQUIRE(nullptr, s.heads == 1 && s.vdim == 1, "layer %d: the element-wise recurrence has heads = vdim = 1", i);
   } else if (s.mixer == L3_MIX_SOFTMAX) {
@@ -94,6 +105,9 @@ extern "C" int l3_create_stack(const L3StackConfig* c, const L3LayerSpec* specs,
           "bad loop bounds");
   REQUIRE(nullptr, !c->norm_input || c->side_dim == 0, "pre-norm stacks have no per-layer token input");
   REQUIRE(nullptr, c->norm_input || (!c->token_shift && !c->norm_scalar), "token shift and single-weight norms are built for pre-norm stacks");
+  REQUIRE(nullptr, !c->parallel || (c->norm_input && !c->token_shift && !c->norm_scalar && c->loop_times == 0), "parallel layers are pre-norm layers without token shift, single-weight norms or loops");
+  REQUIRE(nullptr, c->parallel || (!c->norm_center && !c->layer_scale && !c->canon_taps && !c->depth_avg), "centred norms, layer scales, input convolutions and the depth average are built for parallel layers");
+  REQUIRE(nullptr, c->canon_taps >= 0 && c->canon_taps <= 64, "bad canon_taps");
   L3Model* m = new L3Model();
   LayerList* ll = m->ll = new LayerList();
   ll->cfg = *c;
@@ -147,6 +161,32 @@ extern "C" int l3_create_stack(const L3StackConfig* c, const L3LayerSpec* specs,
       if ((e = cudaMemcpy(L.inv_freq, f.data(), f.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess) {
         set_err(nullptr, "rotary table upload: %s", cudaGetErrorString(e)); l3_destroy(m); return L3_ECUDA;
       }
+    } else if (s.mixer == L3_MIX_DIFF) {
+      L.off_q = 0; L.off_k = 2 * H * DK; L.off_v = L.off_k + 2 * G * DK; L.n_in = pad8(L.off_v + G * DV);  // q | k | v
+      AL(L.in_bias, (size_t)L.n_in * 4);
+      cudaMemset(L.in_bias, 0, (size_t)L.n_in * 4);
+      AL(L.q_norm, (size_t)DK * 4);
+      AL(L.k_norm, (size_t)DK * 4);
+      AL(L.lam_vec, (size_t)4 * DK * 4);
+      AL(L.lambda, 4);
+      AL(L.inv_freq, (size_t)std::max(1, s.rot_dims / 2) * 4);
+      std::vector<float> f(std::max(1, s.rot_dims / 2), 0.f);
+      const double two_pi = 6.283185307179586476925286766559;
+      for (int j = 0; j < s.rot_dims / 2; ++j) {
+        double fr = pow(s.rot_base, -2.0 * j / s.rot_dims);
+        if (s.rot_scale_original > 0) {  // wavelength-dependent rescaling
+          const double wl = two_pi / fr, orig = s.rot_scale_original;
+          if (wl > orig / s.rot_scale_low) fr = fr / s.rot_scale_factor;
+          else if (!(wl < orig / s.rot_scale_high)) {
+            const double sm = (orig / wl - s.rot_scale_low) / ((double)s.rot_scale_high - s.rot_scale_low);
+            fr = (1.0 - sm) * fr / s.rot_scale_factor + sm * fr;
+          }
+        }
+        f[j] = (float)fr;
+      }
+      if ((e = cudaMemcpy(L.inv_freq, f.data(), f.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess) {
+        set_err(nullptr, "rotary table upload: %s", cudaGetErrorString(e)); l3_destroy(m); return L3_ECUDA;
+      }
     } else if (s.mixer == L3_MIX_MINGRU) {
       L.off_b = 0; L.off_v = pad8(DK); L.off_g = pad8(L.off_v + DK); L.n_in = pad8(L.off_g + DK);  // z | x | g
       AL(L.in_bias, (size_t)2 * DK * 4);
@@ -180,7 +220,19 @@ extern "C" int l3_create_stack(const L3StackConfig* c, const L3LayerSpec* specs,
     AL(L.w_o, (size_t)W * n_ctx * w);
     AL(L.norm1, (size_t)W * 4);
     if (c->token_shift) AL(L.shift, (size_t)W * 4);
-    if (s.experts > 0) {
+    if (c->layer_scale) { AL(L.ls1, (size_t)W * 4); if (s.ff > 0) AL(L.ls2, (size_t)W * 4); }
+    if (c->canon_taps > 0) { AL(L.canon1, (size_t)W * c->canon_taps * 4); if (s.ff > 0) AL(L.canon2, (size_t)W * c->canon_taps * 4); }
+    if (c->depth_avg) AL(L.dwa, (size_t)(i + 2) * 4);
+    if (s.experts > 0 && s.router_kind == L3_ROUTE_SIGMOID_IN) {
+      L.ff_total = s.experts * s.ff + s.shared_ff;
+      AL(L.w13, (size_t)2 * L.ff_total * W * w);
+      AL(L.w2, (size_t)W * L.ff_total * w);
+      AL(L.router, (size_t)s.experts * W * 4);
+    } else if (s.ff > 0 && s.ff_kind == L3_FF_POLYNORM) {
+      AL(L.w13, (size_t)s.ff * W * w);
+      AL(L.w2, (size_t)W * s.ff * w);
+      AL(L.poly, 4 * 4);
+    } else if (s.experts > 0) {
       AL(L.w13, (size_t)s.experts * s.ff * W * w);
       AL(L.w2, (size_t)W * s.experts * s.ff * w);
       AL(L.norm2, (size_t)W * 4);
@@ -189,7 +241,7 @@ extern "C" int l3_create_stack(const L3StackConfig* c, const L3LayerSpec* specs,
     } else if (s.ff > 0) {
       AL(L.w13, (size_t)2 * s.ff * W * w);
       AL(L.w2, (size_t)W * s.ff * w);
-      AL(L.norm2, (size_t)W * 4);
+      if (!c->parallel) AL(L.norm2, (size_t)W * 4);
     }
     if (sd) {
       AL(L.side_gate, (size_t)sd * W * w);
@@ -198,6 +250,7 @@ extern "C" int l3_create_stack(const L3StackConfig* c, const L3LayerSpec* specs,
     }
     ll->max_in = std::max(ll->max_in, L.n_in);
     ll->max_o = std::max(ll->max_o, std::max(H * DV, H * DK));
+    if (L.ff_total) ll->max_ff = std::max(ll->max_ff, L.ff_total);
     if (s.mixer == L3_MIX_LATENT) ll->max_o = std::max(ll->max_o, H * s.kv_rank);
     ll->max_ff = std::max(ll->max_ff, s.experts > 0 ? s.experts * s.ff : s.ff);
   }
@@ -269,7 +322,36 @@ static bool ll_place(L3Model* m, const std::string& name, LLPlace* p) {
   const L3LayerSpec& s = L.spec;
   const int H = s.heads, G = s.kv_heads, DK = s.dim, DV = s.vdim;
   if (r == "norm1") return norm(L.norm1);
-  if (r == "norm2") return s.ff > 0 && norm(L.norm2);
+  if (r == "norm2") return s.ff > 0 && L.norm2 && norm(L.norm2);
+  if (r == "ls1") return L.ls1 && vec(L.ls1, W, 1.f, 0.2f);
+  if (r == "ls2") return L.ls2 && vec(L.ls2, W, 1.f, 0.2f);
+  if (r == "canon1") return L.canon1 && fmat(L.canon1, W, ll->cfg.canon_taps, 0.3f / (float)ll->cfg.canon_taps);
+  if (r == "canon2") return L.canon2 && fmat(L.canon2, W, ll->cfg.canon_taps, 0.3f / (float)ll->cfg.canon_taps);
+  if (r == "dwa") return L.dwa && vec(L.dwa, li + 2, 1.f / (float)(li + 2), 0.3f / (float)(li + 2));
+  if (L.ff_total) {  // sigmoid-routed gated experts + shared expert: gate / up rows interleaved, expert by expert
+    if (r == "mlp.router") return fmat(L.router, s.experts, W, 3.0f / sqrtf((float)W));
+    int e = -1, n2 = 0;
+    std::string part;
+    int off = -1, width = 0;
+    if (sscanf(r.c_str(), "mlp.e%d.%n", &e, &n2) >= 1 && n2 > 0 && e >= 0 && e < s.experts) { part = r.substr(n2); off = e * s.ff; width = s.ff; }
+    else if (s.shared_ff > 0 && r.compare(0, 11, "mlp.shared.") == 0) { part = r.substr(11); off = s.experts * s.ff; width = s.shared_ff; }
+    if (off >= 0) {
+      if (part == "gate") return mat(L.w13, width, W, 2 * off, 2);
+      if (part == "up") return mat(L.w13, width, W, 2 * off + 1, 2);
+      if (part == "down") {
+        const bool ok = mat((char*)L.w2 + (size_t)off * wb(m), W, width);
+        p->ld = L.ff_total;
+        return ok;
+      }
+    }
+    if (r.compare(0, 4, "mlp.") == 0) return false;
+  }
+  if (L.poly) {
+    if (r == "mlp.up") return mat(L.w13, s.ff, W);
+    if (r == "mlp.down") return mat(L.w2, W, s.ff);
+    if (r == "mlp.act") return vec(L.poly, 4, 0.4f, 0.2f);
+    if (r.compare(0, 4, "mlp.") == 0) return false;
+  }
   if (r == "shift") return L.shift && vec(L.shift, W, 0.5f, 0.5f);
   if (s.experts > 0) {
     const int n = s.experts + s.identity;
@@ -305,6 +387,22 @@ static bool ll_place(L3Model* m, const std::string& name, LLPlace* p) {
     if (r == "mix.uq") { const bool ok = mat(L.w_uq, (int64_t)H * (DK + s.rot_dim), s.q_rank); p->scale *= 2.f; return ok; }
     if (r == "mix.uk") { const bool ok = mat(L.w_uk, (int64_t)H * DK, s.kv_rank); p->scale *= 2.f; return ok; }
     if (r == "mix.uv") return mat(L.w_uv, (int64_t)H * DV, s.kv_rank);
+    return false;
+  }
+  if (s.mixer == L3_MIX_DIFF) {
+    auto bias = [&](int off, int64_t n) { return vec(L.in_bias + off, n, 0.f, 0.2f); };
+    if (r == "mix.q") return seg(L.off_q, (int64_t)2 * H * DK);
+    if (r == "mix.k") return seg(L.off_k, (int64_t)2 * G * DK);
+    if (r == "mix.v") return seg(L.off_v, (int64_t)G * DV);
+    if (r == "mix.q.b") return bias(L.off_q, (int64_t)2 * H * DK);
+    if (r == "mix.k.b") return bias(L.off_k, (int64_t)2 * G * DK);
+    if (r == "mix.v.b") return bias(L.off_v, (int64_t)G * DV);
+    if (r == "mix.q.norm") return vec(L.q_norm, DK, 1.f, 0.1f);
+    if (r == "mix.k.norm") return vec(L.k_norm, DK, 1.f, 0.1f);
+    if (r == "mix.lq1") return vec(L.lam_vec, DK, 0.f, 0.2f);
+    if (r == "mix.lk1") return vec(L.lam_vec + DK, DK, 0.f, 0.2f);
+    if (r == "mix.lq2") return vec(L.lam_vec + 2 * DK, DK, 0.f, 0.2f);
+    if (r == "mix.lk2") return vec(L.lam_vec + 3 * DK, DK, 0.f, 0.2f);
     return false;
   }
   if (s.mixer == L3_MIX_MINGRU) {
@@ -366,17 +464,37 @@ static std::vector<std::string> ll_expected(const L3Model* m) {
     if (ll->cfg.token_shift) names.push_back("shift");
     if (s.mixer == L3_MIX_LATENT) names.insert(names.end(), {"mix.dq", "mix.dq.norm", "mix.uq", "mix.dkv", "mix.dkv.norm", "mix.uk", "mix.uv", "mix.g"});
     else if (s.mixer == L3_MIX_MINGRU) names.insert(names.end(), {"mix.z", "mix.z.b", "mix.x", "mix.x.b", "mix.g"});
+    else if (s.mixer == L3_MIX_DIFF) names.insert(names.end(), {"mix.q", "mix.q.b", "mix.k", "mix.k.b", "mix.v", "mix.v.b", "mix.q.norm", "mix.k.norm",
+                                                                "mix.lq1", "mix.lk1", "mix.lq2", "mix.lk2"});
     else if (s.mixer == L3_MIX_SOFTMAX) names.insert(names.end(), {"mix.q", "mix.k", "mix.g", "mix.q.norm", "mix.k.norm"});
     else if (s.mixer == L3_MIX_DECAY_LINEAR) names.insert(names.end(), {"mix.q", "mix.k", "mix.v", "mix.g", "mix.norm"});
     else names.insert(names.end(), {"mix.q", "mix.k", "mix.v", "mix.b", "mix.a1", "mix.a2", "mix.g1", "mix.g2", "mix.norm",
                                     "mix.A_log", "mix.dt_bias", "mix.q.conv", "mix.k.conv", "mix.v.conv"});
-    if (s.experts > 0) {
+    const LLLayer& Lx = ll->layers[i];
+    if (Lx.ls1) names.push_back("ls1");
+    if (Lx.ls2) names.push_back("ls2");
+    if (Lx.canon1) names.push_back("canon1");
+    if (Lx.canon2) names.push_back("canon2");
+    if (Lx.dwa) names.push_back("dwa");
+    if (Lx.ff_total) {
+      names.push_back("mlp.router");
+      for (int e = 0; e <= s.experts; ++e) {
+        if (e == s.experts && s.shared_ff == 0) break;
+        const std::string ep = p + (e == s.experts ? std::string("mlp.shared.") : "mlp.e" + std::to_string(e) + ".");
+        v.push_back(ep + "gate"); v.push_back(ep + "up"); v.push_back(ep + "down");
+      }
+    } else if (Lx.poly) {
+      names.insert(names.end(), {"mlp.up", "mlp.down", "mlp.act"});
+    } else if (s.experts > 0) {
       names.insert(names.end(), {"norm2", "mlp.router", "mlp.correction"});
       for (int e = 0; e < s.experts; ++e) {
         v.push_back(p + "mlp.e" + std::to_string(e) + ".up");
         v.push_back(p + "mlp.e" + std::to_string(e) + ".down");
       }
-    } else if (s.ff > 0) names.insert(names.end(), {"norm2", "mlp.gate", "mlp.up", "mlp.down"});
+    } else if (s.ff > 0) {
+      if (Lx.norm2) names.push_back("norm2");
+      names.insert(names.end(), {"mlp.gate", "mlp.up", "mlp.down"});
+    }
     if (ll->cfg.side_dim) names.insert(names.end(), {"side.gate", "side.proj", "side.norm"});
     for (auto nme : names) v.push_back(p + nme);
   }
@@ -441,15 +559,19 @@ int ll_finalize(L3Model* m) {
     if (!ll->loaded.count(name)) { set_err(m, "tensor '%s' was never loaded", name.c_str()); return L3_ESTATE; }
   if (m->stage) { cudaFree(m->stage); m->stage = nullptr; }
   const size_t kvb = m->bf16 ? 2 : 4;
-  int max_rq = 1, max_rk = 1, max_rv = 1, max_rg = 1, max_h = 1, max_aux = 1, max_qlat = 0, max_top = 0, max_exp = 0, max_hid = 1;
+  int max_rq = 1, max_rk = 1, max_rv = 1, max_rg = 1, max_h = 1, max_aux = 1, max_qlat = 0, max_top = 0, max_exp = 0, max_hid = 1, max_gu = 0;
   for (size_t ri = 0; ri < ll->runs.size(); ++ri) {
     const LLLayer& L = ll->layers[ll->runs[ri].layer];
     LLState& St = ll->state[ri];
     const L3LayerSpec& s = L.spec;
     const int H = s.heads, G = s.kv_heads, DK = s.dim, DV = s.vdim;
     if (ll->cfg.token_shift) CK(m, cudaMalloc((void**)&St.hprev, (size_t)m->maxB * m->D * 4));
+    if (ll->cfg.canon_taps > 1) CK(m, cudaMalloc((void**)&St.conv_tail, (size_t)m->maxB * m->D * (ll->cfg.canon_taps - 1) * 4));
     if (s.mixer == L3_MIX_LATENT) {
       CK(m, cudaMalloc(&St.lat, (size_t)m->maxB * m->M * (s.kv_rank + s.rot_dim) * kvb));
+    } else if (s.mixer == L3_MIX_DIFF) {
+      CK(m, cudaMalloc(&St.ck, (size_t)m->maxB * 2 * G * m->M * DK * kvb));
+      CK(m, cudaMalloc(&St.cv, (size_t)m->maxB * G * m->M * DV * kvb));
     } else if (s.mixer == L3_MIX_SOFTMAX) {
       const size_t bytes = (size_t)m->maxB * G * m->M * DK * kvb;
       CK(m, cudaMalloc(&St.ck, bytes));
@@ -467,6 +589,9 @@ int ll_finalize(L3Model* m) {
     const int H = s.heads, G = s.kv_heads, DK = s.dim, DV = s.vdim;
     if (s.mixer == L3_MIX_SOFTMAX) {
       max_rq = std::max(max_rq, H * DK);
+    } else if (s.mixer == L3_MIX_DIFF) {
+      max_rq = std::max(max_rq, 2 * H * DK);
+      LAUNCH(m, launch_diff_lambda(L.lam_vec, DK, s.diff, L.lambda, m->stream));
     } else if (s.mixer == L3_MIX_GATED_DELTA) {
       max_rq = std::max(max_rq, G * DK); max_rk = std::max(max_rk, G * DK); max_rv = std::max(max_rv, H * DV);
       max_rg = std::max(max_rg, H * DK); max_h = std::max(max_h, H); max_aux = std::max(max_aux, H * DK + H * DV);
@@ -475,7 +600,8 @@ int ll_finalize(L3Model* m) {
       max_aux = std::max(max_aux, s.q_rank);
       max_qlat = std::max(max_qlat, H * (s.kv_rank + s.rot_dim));
     }
-    if (s.experts > 0) { max_top = std::max(max_top, s.top); max_exp = std::max(max_exp, s.experts); max_hid = std::max(max_hid, s.top * s.ff); }
+    if (s.experts > 0) { max_top = std::max(max_top, s.top); max_exp = std::max(max_exp, s.experts); max_hid = std::max(max_hid, (s.top + 1) * std::max(s.ff, s.shared_ff)); }
+    max_gu = std::max(max_gu, 2 * L.ff_total);
   }
   const int W = m->D, sd = ll->cfg.side_dim;
   const int64_t want = (int64_t)m->maxB * m->M;
@@ -498,6 +624,16 @@ int ll_finalize(L3Model* m) {
   CK(m, cudaMalloc((void**)&ll->o, ct * ll->max_o * 4));
   CK(m, cudaMalloc((void**)&ll->sg, ct * std::max(1, sd) * 4));
   if (max_qlat) CK(m, cudaMalloc((void**)&ll->qlat, ct * max_qlat * 4));
+  if (ll->cfg.parallel) {
+    if (ll->cfg.depth_avg) CK(m, cudaMalloc((void**)&ll->Xs, (size_t)(ll->cfg.n_layers + 1) * ct * W * 4));
+    if (ll->cfg.canon_taps > 0) {
+      CK(m, cudaMalloc((void**)&ll->hn, ct * W * 4));
+      CK(m, cudaMalloc((void**)&ll->hf, ct * W * 4));
+    }
+    CK(m, cudaMalloc((void**)&ll->y1, ct * W * 4));
+    CK(m, cudaMalloc((void**)&ll->y2, ct * W * 4));
+    if (max_gu) CK(m, cudaMalloc((void**)&ll->moe_gu, ct * max_gu * 4));
+  }
   if (max_top) {
     CK(m, cudaMalloc((void**)&ll->moe_sel, ct * max_top * 4));
     CK(m, cudaMalloc((void**)&ll->moe_w, ct * max_top * 4));
@@ -523,11 +659,12 @@ int ll_finalize(L3Model* m) {
     CK(m, cudaMalloc(&m->xlast16, (size_t)m->maxB * W * 2));
     CK(m, cudaMalloc(&ll->sg16, ct * std::max(1, sd) * 2));
     if (max_qlat) CK(m, cudaMalloc(&ll->aux16, ct * max_aux * 2));
+    if (ll->hf) CK(m, cudaMalloc(&ll->hf16, ct * W * 2));
   }
   m->max_split = 32;
   int max_hn = 1, max_hd = 1;
   for (auto& L : ll->layers)
-    if (L.spec.mixer == L3_MIX_SOFTMAX) { max_hn = std::max(max_hn, L.spec.heads); max_hd = std::max(max_hd, L.spec.dim); }
+    if (L.spec.mixer == L3_MIX_SOFTMAX || L.spec.mixer == L3_MIX_DIFF) { max_hn = std::max(max_hn, L.spec.heads); max_hd = std::max(max_hd, L.spec.dim); }
     else if (L.spec.mixer == L3_MIX_LATENT) { max_hn = std::max(max_hn, L.spec.heads); max_hd = std::max(max_hd, L.spec.kv_rank); }
   CK(m, cudaMalloc((void**)&m->part_o, (size_t)m->maxB * max_hn * m->max_split * max_hd * 4));
   CK(m, cudaMalloc((void**)&m->part_ml, (size_t)m->maxB * max_hn * m->max_split * 2 * 4));
@@ -565,8 +702,10 @@ void ll_destroy(L3Model* m) {
     fr(L.norm1); fr(L.norm2); fr(L.side_norm); fr(L.mix_norm); fr(L.q_norm); fr(L.k_norm); fr(L.conv_w);
     fr(L.A_log); fr(L.dt_bias); fr(L.decay);
     fr(L.w_uq); fr(L.w_uk); fr(L.w_uv); fr(L.inv_freq); fr(L.in_bias); fr(L.shift); fr(L.router); fr(L.correction);
+    fr(L.canon1); fr(L.canon2); fr(L.ls1); fr(L.ls2); fr(L.dwa); fr(L.lam_vec); fr(L.lambda); fr(L.poly);
   }
   for (auto& St : ll->state) { fr(St.ck); fr(St.cv); fr(St.S); fr(St.conv_tail); fr(St.lat); fr(St.hprev); }
+  fr(ll->Xs); fr(ll->hn); fr(ll->hf); fr(ll->hf16); fr(ll->y1); fr(ll->y2); fr(ll->moe_gu);
   fr(ll->loop_step); fr(ll->qlat); fr(ll->aux16); fr(ll->moe_sel); fr(ll->moe_w); fr(ll->moe_dense); fr(ll->moe_idw);
   fr(ll->pin); fr(ll->aux); fr(ll->rk); fr(ll->rv); fr(ll->rg); fr(ll->rbeta); fr(ll->o); fr(ll->sg); fr(ll->sg16); fr(ll->x2); fr(ll->chunk_ws);
   delete ll;
@@ -580,6 +719,17 @@ int ll_reset_slots(L3Model* m, int slot0, int n, bool kv_too) {
     const L3LayerSpec& s = ll->layers[ll->runs[ri].layer].spec;
     LLState& St = ll->state[ri];
     if (St.hprev) CK(m, cudaMemsetAsync(St.hprev + (size_t)slot0 * m->D, 0, (size_t)n * m->D * 4, m->stream));
+    if (s.mixer == L3_MIX_DIFF) {
+      if (St.conv_tail) {  // zeros ahead of a sequence's first token
+        const size_t pc = (size_t)m->D * (ll->cfg.canon_taps - 1);
+        CK(m, cudaMemsetAsync(St.conv_tail + slot0 * pc, 0, n * pc * 4, m->stream));
+      }
+      if (!kv_too) continue;  // rows past a slot's position are never read
+      const size_t pk = (size_t)2 * s.kv_heads * m->M * s.dim * kvb, pv = (size_t)s.kv_heads * m->M * s.vdim * kvb;
+      CK(m, cudaMemsetAsync((char*)St.ck + slot0 * pk, 0, n * pk, m->stream));
+      CK(m, cudaMemsetAsync((char*)St.cv + slot0 * pv, 0, n * pv, m->stream));
+      continue;
+    }
     if (s.mixer == L3_MIX_LATENT) {
       if (!kv_too) continue;  // rows past a slot's position are never read: a new sequence overwrites them
       const size_t per = (size_t)m->M * (s.kv_rank + s.rot_dim) * kvb;
@@ -632,7 +782,7 @@ extern "C" int l3_read_state(L3Model* m, int layer, int slot, float* S_out, floa
   const LLLayer& L = m->ll->layers[m->ll->runs[layer].layer];
   const LLState& St = m->ll->state[layer];
   const L3LayerSpec& s = L.spec;
-  REQUIRE(m, s.mixer != L3_MIX_SOFTMAX, "layer run %d keeps a KV cache, not a recurrent state (l3_read_cache)", layer);
+  REQUIRE(m, s.mixer != L3_MIX_SOFTMAX && s.mixer != L3_MIX_DIFF, "layer run %d keeps a KV cache, not a recurrent state (l3_read_cache)", layer);
   CK(m, cudaSetDevice(m->cfg.device));
   CK(m, cudaStreamSynchronize(m->stream));
   if (s.mixer == L3_MIX_LATENT) {
@@ -830,6 +980,80 @@ static int ll_enqueue_prenorm(L3Model* m, int B, int L, float* d_resid) {
   return L3_OK;
 }
 
+// ------------------------------------------------------------------------------ parallel layers
+// h = norm1(x);  X_new = x + ls1 * mixer(h + conv1(h)) + ls2 * ff(h + conv2(h));  x <- sum_j dwa[j] X_j (depth average).
+// One norm per layer; both sublayers' output projections store into y1 / y2 and ONE kernel forms the layer's result,
+// keeps it for the later layers' averages and writes the stream that goes on.
+static int ll_enqueue_parallel(L3Model* m, int B, int L, float* d_resid) {
+  LayerList* ll = m->ll;
+  const int ntok = B * L, W = m->D, T = ll->cfg.canon_taps;
+  const float eps = ll->cfg.norm_eps;
+  int* d_pos = m->d_scal + 0;
+  const int64_t xs = (int64_t)m->cap_tok * W;
+  int rc;
+  ll->xcur = m->x;
+  if (ll->Xs) CK(m, cudaMemcpyAsync(ll->Xs, m->x, (size_t)ntok * W * 4, cudaMemcpyDeviceToDevice, m->stream));
+  for (int ri = 0; ri < (int)ll->runs.size(); ++ri) {
+    LLLayer& Ly = ll->layers[ll->runs[ri].layer];
+    LLState& St = ll->state[ri];
+    const L3LayerSpec& s = Ly.spec;
+    const int H = s.heads, G = s.kv_heads, DK = s.dim, DV = s.vdim;
+    const bool has_ff = s.ff > 0;
+    float *hm = m->xn, *hf = m->xn;
+    bf16 *hm16 = (bf16*)m->xn16, *hf16 = (bf16*)m->xn16;  // null in fp32 mode
+    if (T > 0) {
+      hf = ll->hf; hf16 = (bf16*)ll->hf16;
+      LAUNCH(m, launch_layernorm_rows(m->x, Ly.norm1, eps, ll->cfg.norm_center, ntok, W, 1, 0, nullptr, ll->hn, nullptr, m->stream));
+      LAUNCH(m, launch_canon(ll->hn, St.conv_tail, Ly.canon1, has_ff ? Ly.canon2 : nullptr, B, L, W, T, hm, hm16, has_ff ? hf : nullptr, hf16, m->stream));
+      if (T > 1) LAUNCH(m, launch_conv_tail(St.conv_tail, ll->hn, W, B, L, W, T - 1, m->stream));
+    } else {
+      LAUNCH(m, launch_layernorm_rows(m->x, Ly.norm1, eps, ll->cfg.norm_center, ntok, W, 1, 0, nullptr, hm, hm16, m->stream));
+    }
+    if (s.mixer != L3_MIX_DIFF) { set_err(m, "mixer %d is not built for parallel layers", s.mixer); return L3_EINVAL; }
+    if ((rc = ll_linear(m, Ly.w_in, hm, hm16, 0, ntok, Ly.n_in, W, EPI_STORE, store_to(ll->pin, nullptr, Ly.n_in))) != L3_OK) return rc;
+    DiffPrepArgs pa{};
+    pa.proj = ll->pin; pa.ld = Ly.n_in; pa.q_off = Ly.off_q; pa.k_off = Ly.off_k; pa.v_off = Ly.off_v; pa.bias = Ly.in_bias;
+    pa.wq = Ly.q_norm; pa.wk = Ly.k_norm; pa.eps = eps; pa.inv_freq = Ly.inv_freq; pa.q_out = m->q; pa.cache_k = St.ck; pa.cache_v = St.cv;
+    pa.pos_ptr = d_pos; pa.L = L; pa.H = H; pa.G = G; pa.DK = DK; pa.DV = DV; pa.M = m->M; pa.rot_dims = s.rot_dims;
+    LAUNCH(m, launch_diff_prep(pa, ntok, m->bf16, m->stream));
+    DiffAttnArgs at{};
+    at.q = m->q; at.cache_k = St.ck; at.cache_v = St.cv; at.out = m->ctx; at.out16 = (bf16*)m->ctx16; at.lambda = Ly.lambda;
+    at.pos_ptr = d_pos; at.scale = s.scale; at.diff = s.diff; at.eps = eps; at.window = s.window;
+    at.B = B; at.L = L; at.H = H; at.G = G; at.DK = DK; at.DV = DV; at.M = m->M;
+    LAUNCH(m, launch_diff_attn(at, m->bf16, m->stream));
+    if ((rc = ll_linear(m, Ly.w_o, m->ctx, m->ctx16, 0, ntok, W, H * DV, EPI_STORE, store_to(ll->y1, nullptr, W))) != L3_OK) return rc;
+    if (Ly.ff_total) {
+      const int E = s.experts, ff = s.ff, F = Ly.ff_total;
+      const bool few = ntok <= 8;  // few rows read only their chosen experts' weights; many share one GEMM over all experts
+      MoeRouteArgs ra{};
+      ra.h = hf; ra.router = Ly.router; ra.correction = nullptr; ra.D = W; ra.E = E; ra.I = 0; ra.top = s.top;
+      ra.groups = 1; ra.keep = 1; ra.kind = 1; ra.scale = 1.0f;
+      ra.sel = ll->moe_sel; ra.w = ll->moe_w; ra.dense = few ? nullptr : ll->moe_dense; ra.idw = ll->moe_idw;
+      LAUNCH(m, launch_moe_route(ra, ntok, m->stream));
+      if (few) {
+        LAUNCH(m, launch_moe_glu_rows(hf, Ly.w13, Ly.w2, m->bf16, ll->moe_sel, ll->moe_w, ntok, W, E, ff, s.shared_ff, s.top, m->h, ll->y2, m->stream));
+        m->launch_acc += 1;
+      } else {
+        if ((rc = ll_linear(m, Ly.w13, hf, hf16, 0, ntok, 2 * F, W, EPI_STORE, store_to(ll->moe_gu, nullptr, 2 * F))) != L3_OK) return rc;
+        LAUNCH(m, launch_moe_glu_act(ll->moe_gu, ll->moe_dense, ntok, E, ff, s.shared_ff, m->h, (bf16*)m->h16, m->stream));
+        if ((rc = ll_linear(m, Ly.w2, m->h, m->h16, 0, ntok, W, F, EPI_STORE, store_to(ll->y2, nullptr, W))) != L3_OK) return rc;
+      }
+    } else if (Ly.poly) {
+      if ((rc = ll_linear(m, Ly.w13, hf, hf16, 0, ntok, s.ff, W, EPI_STORE, store_to(m->h, nullptr, s.ff))) != L3_OK) return rc;
+      LAUNCH(m, launch_polynorm(m->h, Ly.poly, eps, ntok, s.ff, (bf16*)m->h16, m->stream));
+      if ((rc = ll_linear(m, Ly.w2, m->h, m->h16, 0, ntok, W, s.ff, EPI_STORE, store_to(ll->y2, nullptr, W))) != L3_OK) return rc;
+    } else if (has_ff) {
+      EpiArgs e = store_to(m->h, m->h16, s.ff);
+      e.act = ll->cfg.glu_act;
+      if ((rc = ll_linear(m, Ly.w13, hf, hf16, 0, ntok, 2 * s.ff, W, EPI_SWIGLU, e)) != L3_OK) return rc;
+      if ((rc = ll_linear(m, Ly.w2, m->h, m->h16, 0, ntok, W, s.ff, EPI_STORE, store_to(ll->y2, nullptr, W))) != L3_OK) return rc;
+    }
+    LAUNCH(m, launch_parallel_combine(m->x, ll->y1, has_ff ? ll->y2 : nullptr, Ly.ls1, Ly.ls2, ll->Xs, xs, Ly.dwa, ri + 1, ntok, W, m->stream));
+    if (d_resid) CK(m, cudaMemcpyAsync(d_resid + (size_t)ri * ntok * W, m->x, (size_t)ntok * W * 4, cudaMemcpyDeviceToDevice, m->stream));
+  }
+  return L3_OK;
+}
+
 // ------------------------------------------------------------------------------ the layers of one chunk
 int ll_enqueue_layers(L3Model* m, const int32_t* d_ids, int ids_ld, int ids_off, int B, int L, float* d_resid) {
   LayerList* ll = m->ll;
@@ -843,6 +1067,7 @@ int ll_enqueue_layers(L3Model* m, const int32_t* d_ids, int ids_ld, int ids_off,
   ll->xcur = m->x;
   ll->xalt = ll->x2;
   LLPending pd;
+  if (ll->cfg.parallel) return ll_enqueue_parallel(m, B, L, d_resid);
   // rows <= 8 never reach a tensor-core projection of the residual stream: no mirror needed
   if (x16 && !linear_rows_supported(ntok, W)) LAUNCH(m, launch_to_bf16(m->x, (int64_t)ntok * W, x16, m->stream));
   if (ll->cfg.norm_input) return ll_enqueue_prenorm(m, B, L, d_resid);
@@ -949,6 +1174,9 @@ int ll_ensure_head_rows(L3Model* m, int n) {
 
 int ll_enqueue_head(L3Model* m, int B, int L, const int32_t* d_rows, int n_rows) {
   const int rows = d_rows ? n_rows : B;
-  LAUNCH(m, launch_rmsnorm_rows(m->ll->xcur, m->norm_final, m->ll->cfg.norm_eps, rows, m->D, L, L - 1, d_rows, m->xlast, (bf16*)m->xlast16, m->stream));
+  if (m->ll->cfg.norm_center)
+    LAUNCH(m, launch_layernorm_rows(m->ll->xcur, m->norm_final, m->ll->cfg.norm_eps, 1, rows, m->D, L, L - 1, d_rows, m->xlast, (bf16*)m->xlast16, m->stream));
+  else
+    LAUNCH(m, launch_rmsnorm_rows(m->ll->xcur, m->norm_final, m->ll->cfg.norm_eps, rows, m->D, L, L - 1, d_rows, m->xlast, (bf16*)m->xlast16, m->stream));
   return ll_linear(m, m->lm_head, m->xlast, m->xlast16, 0, rows, m->VS, m->D, EPI_STORE, store_to(m->logits, nullptr, m->VS));
 }

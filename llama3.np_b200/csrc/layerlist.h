@@ -39,6 +39,14 @@ struct LLLayer {
   // mixture of experts: w13 = [experts * ff, width] up rows expert by expert, w2 = [width, experts * ff]
   float* router = nullptr;      // [experts + identity, width] fp32
   float* correction = nullptr;  // [experts + identity]
+  // parallel layers: convolutions ahead of the sublayers [width, taps], layer scales [width], depth-average weights [layer + 2]
+  float *canon1 = nullptr, *canon2 = nullptr, *ls1 = nullptr, *ls2 = nullptr, *dwa = nullptr;
+  // differential attention: w_in = q | k | v rows with in_bias [n_in]; q_norm / k_norm [dim]; lam_vec = lq1 | lk1 | lq2 | lk2
+  float *lam_vec = nullptr, *lambda = nullptr;
+  float* poly = nullptr;        // PolyNorm coefficients (a, b, c, e); w13 is then the plain up matrix [ff, width]
+  // sigmoid-routed gated experts: w13 = [2 (experts ff + shared_ff), width] rows interleaved (gate_j, up_j), expert by
+  // expert, the shared expert last; w2 = [width, experts ff + shared_ff]
+  int ff_total = 0;
 };
 
 // What one layer RUN keeps per sequence slot (a layer inside the loop has one of these per pass).
@@ -48,6 +56,8 @@ struct LLState {
   float* conv_tail = nullptr;         // gated delta: [maxB, channels, taps - 1]
   void* lat = nullptr;                // latent attention: [maxB, M, kv_rank + rot_dim] of KVT
   float* hprev = nullptr;             // token shift: [maxB, width] the last token's normed mixer input
+  // differential attention: ck [maxB, 2 kv_heads, M, dim] (head g, map m at 2 g + m), cv [maxB, kv_heads, M, vdim];
+  // parallel layers with a convolution: conv_tail [maxB, width, taps - 1] the last rows of the layer's normed input
 };
 
 struct LLRun {
@@ -77,6 +87,12 @@ struct LayerList {
   void* aux16 = nullptr;                   // bf16 mirror of aux (the query latent)
   float *moe_w = nullptr, *moe_dense = nullptr, *moe_idw = nullptr;  // [rows, top] | [rows, experts] | [rows]
   int32_t* moe_sel = nullptr;              // [rows, top]
+  // parallel layers
+  float* Xs = nullptr;                     // [n_layers + 1][cap_tok, width] embedding output and every layer's own result
+  float *hn = nullptr, *hf = nullptr;      // normed rows ahead of the convolutions; the feed-forward's input
+  void* hf16 = nullptr;
+  float *y1 = nullptr, *y2 = nullptr;      // the two sublayers' results [cap_tok, width]
+  float* moe_gu = nullptr;                 // [cap_tok, 2 ff_total] gate | up of every expert
   int max_in = 0, max_o = 0, max_ff = 0;
   int head_rows = 0;  // rows the LM head's buffers hold
 };

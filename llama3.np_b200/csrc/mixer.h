@@ -135,12 +135,61 @@ cudaError_t launch_latent_attn(const LatentAttnArgs& a, bool kv_bf16, cudaStream
 cudaError_t launch_mingru_scan(float* proj, int ld, int z_off, int x_off, int g_off, const float* bias, float* S, int B,
                                int L, int n, float* out, bf16* out16, cudaStream_t s);
 
+// ---- parallel layers (parallel_ops.cu)
+// out[r] = (x[src] - mean) / sqrt(var + eps) * w  (center 0: x / rms * w); source rows as launch_rmsnorm_rows
+cudaError_t launch_layernorm_rows(const float* x, const float* w, float eps, int center, int rows, int D, int src_mul,
+                                  int src_add, const int32_t* src_rows, float* out, bf16* out16, cudaStream_t s);
+// out_s[t] = h[t] + sum_j w_s[:, j] h[t - T + 1 + j] for s = 1, 2 (out2 null: one sublayer); h [B * L, D]; w_s [D, T];
+// tail [maxB, D, T - 1] holds the rows ahead of the call, oldest first (moved on by launch_conv_tail afterwards)
+cudaError_t launch_canon(const float* h, const float* tail, const float* w1, const float* w2, int B, int L, int D, int T,
+                         float* out1, bf16* out1_16, float* out2, bf16* out2_16, cudaStream_t s);
+// z[r] <- a N(z) + b N(z^2) + c N(z^3) + e in place (+ bf16 mirror), N = RMS norm over the n values of a row; coef = (a, b, c, e)
+cudaError_t launch_polynorm(float* z, const float* coef, float eps, int rows, int n, bf16* out16, cudaStream_t s);
+// v = x + ls1 * y1 + ls2 * y2 (y2 null: no second sublayer; ls null: ones).  Xs null: x <- v.  Else Xs[n_prev] <- v and
+// x <- sum_(j < n_prev) dwa[j] Xs[j] + dwa[n_prev] v, Xs[j] at Xs + j * x_stride
+cudaError_t launch_parallel_combine(float* x, const float* y1, const float* y2, const float* ls1, const float* ls2, float* Xs,
+                                    int64_t x_stride, const float* dwa, int n_prev, int rows, int D, cudaStream_t s);
+
+// ---- differential sliding-window attention (attn_diff.cu)
+struct DiffPrepArgs {
+  const float* proj;     // [rows, ld]: q (H heads of [map 1 | map 2], DK each) at q_off, k (G heads likewise) at k_off, v (G x DV) at v_off
+  int ld, q_off, k_off, v_off;
+  const float* bias;     // [ld] biases of the projection's columns
+  const float *wq, *wk;  // [DK] norm weights shared by all heads and maps
+  float eps;
+  const float* inv_freq; // [rot_dims / 2]
+  float* q_out;          // [rows, H, 2, DK]
+  void* cache_k;         // [maxB, 2 G, M, DK] of KVT: head g, map m at index 2 g + m
+  void* cache_v;         // [maxB, G, M, DV]
+  const int* pos_ptr;
+  int L, H, G, DK, DV, M, rot_dims;
+};
+cudaError_t launch_diff_prep(const DiffPrepArgs& a, int rows, bool kv_bf16, cudaStream_t s);
+// out = exp(v[0:n] . v[n:2n]) - exp(v[2n:3n] . v[3n:4n]) + diff
+cudaError_t launch_diff_lambda(const float* vecs, int n, float diff, float* out, cudaStream_t s);
+struct DiffAttnArgs {
+  const float* q;        // [B * L, H, 2, DK]
+  const void* cache_k;   // [maxB, 2 G, M, DK]
+  const void* cache_v;   // [maxB, G, M, DV]
+  float* out;            // [B * L, H, DV] (+ bf16 mirror, may be null)
+  bf16* out16;
+  const float* lambda;   // device scalar
+  const int* pos_ptr;    // token t of the call sits at *pos_ptr + t
+  float scale, diff, eps;
+  int window;            // query i sees keys j with 0 <= i - j < window; 0: every key up to i
+  int B, L, H, G, DK, DV, M;
+};
+bool diff_attn_supported(int DK, int DV);
+bool diff_attn_tiled(int DK, int DV);
+cudaError_t launch_diff_attn(const DiffAttnArgs& a, bool kv_bf16, cudaStream_t s);
+
 // ---- mixture of experts (moe.cu)
 struct MoeRouteArgs {
   const float* h;        // [rows, D] router input
   const float* router;   // [E + I, D] fp32
   const float* correction;
   int D, E, I, top, groups, keep;
+  int kind;              // 0: softmax scores + correction + groups; 1: scores = sigmoid(logit), the top scores win, weight = score
   float scale;
   int32_t* sel;          // [rows, top] chosen slots, best first
   float* w;              // [rows, top] their weights
@@ -157,3 +206,15 @@ cudaError_t launch_moe_identity(float* x, const float* h, const float* idw, int 
 cudaError_t launch_moe_rows(const float* h, const void* w_up, const void* w_down, bool w_bf16, const int32_t* sel,
                             const float* w, const float* idw, int rows, int D, int E, int ff, int top, float* hid, float* x,
                             cudaStream_t s);
+
+// Gated experts whose routing weight multiplies their INPUT (L3_ROUTE_SIGMOID_IN): expert e = down_e(silu(w gate_e h) * (w up_e h)).
+// Weights: w_gu [2 (E ff + sff), D] rows interleaved (gate_j, up_j), expert e at rows [2 e ff, 2 (e + 1) ff), the shared expert
+// (width sff, weight 1, every token; sff 0: none) behind them; w_down [D, E ff + sff].
+// masked-dense path: gu [rows, 2 F] (F = E ff + sff) -> hid [rows, F] = silu(w g) * (w u), zero where the row did not choose the expert
+cudaError_t launch_moe_glu_act(const float* gu, const float* dense, int rows, int E, int ff, int sff, float* hid, bf16* hid16,
+                               cudaStream_t s);
+// few rows: only the chosen experts' (and the shared expert's) weights are read.  hid [rows * (top + 1), max(ff, sff)] scratch;
+// y[r] = sum over the row's experts of down_e hid
+cudaError_t launch_moe_glu_rows(const float* h, const void* w_gu, const void* w_down, bool w_bf16, const int32_t* sel,
+                                const float* w, int rows, int D, int E, int ff, int sff, int top, float* hid, float* y,
+                                cudaStream_t s);

@@ -56,6 +56,10 @@ __global__ void __launch_bounds__(256) moe_route_kernel(MoeRouteArgs a) {
   }
   __syncthreads();
   if (warp != 0) return;
+  if (a.kind == 1) {  // independent sigmoid scores; the largest win
+    for (int e = lane; e < n; e += 32) { const float sc = 1.0f / (1.0f + expf(-s_score[e])); s_score[e] = sc; s_choice[e] = sc; }
+    __syncwarp();
+  } else {
   float mx = -INFINITY;
   for (int e = lane; e < n; e += 32) mx = fmaxf(mx, s_score[e]);
   mx = warp_max(mx);
@@ -69,6 +73,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(MoeRouteArgs a) {
     s_choice[e] = sc + a.correction[e];
   }
   __syncwarp();
+  }
   const int per = n / a.groups;
   if (a.groups > 1 && a.keep < a.groups) {
     for (int g = lane; g < a.groups; g += 32) {
@@ -190,7 +195,94 @@ __global__ void __launch_bounds__(256) moe_down_rows_kernel(const float* __restr
   if (lane == 0) x[(size_t)row * D + i] += acc + idw[row] * h[(size_t)row * D + i];
 }
 
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+
+__global__ void moe_glu_act_kernel(const float* __restrict__ gu, const float* __restrict__ dense, int64_t n, int E, int ff, int sff,
+                                   float* __restrict__ hid, bf16* __restrict__ hid16) {
+  pdl_launch();
+  pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int64_t F = (int64_t)E * ff + sff;
+  const int64_t r = i / F;
+  const int64_t c = i - r * F;
+  const float w = c < (int64_t)E * ff ? dense[r * E + c / ff] : 1.0f;
+  float o = 0.f;
+  if (w != 0.f) {
+    const float2 p = *reinterpret_cast<const float2*>(gu + 2 * i);
+    o = silu_f(w * p.x) * (w * p.y);
+  }
+  hid[i] = o;
+  if (hid16) hid16[i] = __float2bfloat16_rn(o);
+}
+
+// grid (ceil(max(ff, sff) / 8), rows * (top + 1)): slot k < top of a row is its k-th chosen expert, slot top the shared expert
+template <typename WT>
+__global__ void __launch_bounds__(256) moe_glu_up_rows_kernel(const float* __restrict__ h, const WT* __restrict__ w_gu,
+                                                              const int32_t* __restrict__ sel, const float* __restrict__ wsel,
+                                                              int D, int E, int ff, int sff, int top, int hs,
+                                                              float* __restrict__ hid) {
+  pdl_launch();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int slot = blockIdx.y, row = slot / (top + 1), k = slot - row * (top + 1);
+  const int j = blockIdx.x * 8 + warp;
+  const bool shared = k == top;
+  const int e = shared ? E : sel[row * top + k];
+  const int width = shared ? sff : ff;
+  if (j >= width || e > E || (!shared && e >= E)) return;
+  const float w = shared ? 1.0f : wsel[row * top + k];
+  const WT* wr = w_gu + ((size_t)2 * ((size_t)e * ff + j)) * D;
+  const float* hr = h + (size_t)row * D;
+  const float g = warp_dot(wr, hr, D, lane), u = warp_dot(wr + D, hr, D, lane);
+  if (lane == 0) hid[(size_t)slot * hs + j] = silu_f(w * g) * (w * u);
+}
+
+// grid (ceil(D / 8), rows): y[row, i] = sum over the row's slots of down_e[i] . hid[slot]
+template <typename WT>
+__global__ void __launch_bounds__(256) moe_glu_down_rows_kernel(const WT* __restrict__ w_down, const int32_t* __restrict__ sel,
+                                                                int D, int E, int ff, int sff, int top, int hs,
+                                                                const float* __restrict__ hid, float* __restrict__ y) {
+  pdl_launch();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row = blockIdx.y, i = blockIdx.x * 8 + warp;
+  if (i >= D) return;
+  const size_t F = (size_t)E * ff + sff;
+  float acc = 0.f;
+  for (int k = 0; k <= top; ++k) {
+    const bool shared = k == top;
+    if (shared && sff == 0) break;
+    const int e = shared ? E : sel[row * top + k];
+    if (!shared && e >= E) continue;
+    acc += warp_dot(w_down + (size_t)i * F + (size_t)e * ff, hid + ((size_t)row * (top + 1) + k) * hs, shared ? sff : ff, lane);
+  }
+  if (lane == 0) y[(size_t)row * D + i] = acc;
+}
+
 }  // namespace
+
+cudaError_t launch_moe_glu_act(const float* gu, const float* dense, int rows, int E, int ff, int sff, float* hid, bf16* hid16,
+                               cudaStream_t s) {
+  const int64_t n = (int64_t)rows * ((int64_t)E * ff + sff);
+  return launch_k(moe_glu_act_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, gu, dense, n, E, ff, sff, hid, hid16);
+}
+
+cudaError_t launch_moe_glu_rows(const float* h, const void* w_gu, const void* w_down, bool w_bf16, const int32_t* sel,
+                                const float* w, int rows, int D, int E, int ff, int sff, int top, float* hid, float* y,
+                                cudaStream_t s) {
+  const int hs = ff > sff ? ff : sff;
+  const dim3 gu((hs + 7) / 8, rows * (top + 1)), gd((D + 7) / 8, rows);
+  cudaError_t e;
+  if (w_bf16) {
+    e = launch_k(moe_glu_up_rows_kernel<bf16>, gu, dim3(256), 0, s, h, (const bf16*)w_gu, sel, w, D, E, ff, sff, top, hs, hid);
+    if (e != cudaSuccess) return e;
+    return launch_k(moe_glu_down_rows_kernel<bf16>, gd, dim3(256), 0, s, (const bf16*)w_down, sel, D, E, ff, sff, top, hs, (const float*)hid, y);
+  }
+  e = launch_k(moe_glu_up_rows_kernel<float>, gu, dim3(256), 0, s, h, (const float*)w_gu, sel, w, D, E, ff, sff, top, hs, hid);
+  if (e != cudaSuccess) return e;
+  return launch_k(moe_glu_down_rows_kernel<float>, gd, dim3(256), 0, s, (const float*)w_down, sel, D, E, ff, sff, top, hs, (const float*)hid, y);
+}
 
 cudaError_t launch_moe_route(const MoeRouteArgs& a, int rows, cudaStream_t s) {
   if (a.E + a.I > MOE_MAX_SLOTS || a.groups < 1 || (a.E + a.I) % a.groups) return cudaErrorInvalidValue;

@@ -1,0 +1,150 @@
+// Row kernels of parallel layers (layerlist.cu, L3StackConfig::parallel): one norm per layer, both sublayers read it.
+// Everything here is fp32; the bf16 mirrors feed the tensor-core projections.
+//
+//  * layernorm_rows_kernel    (x - mean) / sqrt(var + eps) * w over chosen rows (var = mean of the squared deviations);
+//                             center = 0 gives the plain RMS norm.  The layers' norm1 and the final norm.
+//  * canon_kernel             the causal convolution over time ahead of each sublayer, for both sublayers at once:
+//                             out_s[t] = h[t] + sum_j w_s[:, j] h[t - T + 1 + j]; rows ahead of the call come from the
+//                             slot's tail (the last T - 1 rows of h, moved on by conv_tail_kernel of mixer_ops.cu)
+//  * polynorm_kernel          a N(z) + b N(z^2) + c N(z^3) + e over a token's feed-forward values, N = RMS norm
+//  * parallel_combine_kernel  X_new = x + ls1 * y1 + ls2 * y2, stored as layer result i + 1, and the stream handed on:
+//                             x = sum_j dwa[j] X_j over the embedding output and every layer result so far
+#include "common.cuh"
+#include "mixer.h"
+
+namespace {
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int w = 0; w < nw; ++w) t += red[w];
+  return t;
+}
+
+__global__ void __launch_bounds__(256) layernorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps,
+                                                             int D, int center, int src_mul, int src_add,
+                                                             const int32_t* __restrict__ src_rows, float* __restrict__ out,
+                                                             bf16* __restrict__ out16) {
+  __shared__ float red[32];
+  pdl_launch();
+  pdl_wait();
+  const size_t r = blockIdx.x;
+  const float* xr = x + (src_rows ? (size_t)src_rows[r] : r * src_mul + src_add) * D;
+  float mean = 0.f;
+  if (center) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) s += xr[i];
+    mean = block_sum(s, red) / (float)D;
+  }
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) { const float v = xr[i] - mean; ss = fmaf(v, v, ss); }
+  const float rinv = 1.0f / sqrtf(block_sum(ss, red) / (float)D + eps);
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const float v = (xr[i] - mean) * rinv * w[i];
+    out[r * D + i] = v;
+    if (out16) out16[r * D + i] = __float2bfloat16_rn(v);
+  }
+}
+
+// one thread per (row, channel); w1 / w2 [D, T], last tap = the current token; tail [maxB, D, T - 1], oldest first
+__global__ void __launch_bounds__(256) canon_kernel(const float* __restrict__ h, const float* __restrict__ tail,
+                                                    const float* __restrict__ w1, const float* __restrict__ w2, int L, int D, int T,
+                                                    int64_t n, float* __restrict__ out1, bf16* __restrict__ out1_16,
+                                                    float* __restrict__ out2, bf16* __restrict__ out2_16) {
+  pdl_launch();
+  pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int64_t r = i / D;
+  const int c = (int)(i - r * D);
+  const int b = (int)(r / L), t = (int)(r - (int64_t)b * L);
+  const float cur = h[i];
+  float a1 = cur, a2 = cur;
+  for (int j = 0; j < T; ++j) {
+    const int v = t - (T - 1) + j;  // row of this call, or (negative) a row of the tail
+    const float hv = v >= 0 ? h[((int64_t)b * L + v) * D + c] : tail[((size_t)b * D + c) * (T - 1) + (T - 1 + v)];
+    a1 = fmaf(w1[(size_t)c * T + j], hv, a1);
+    if (out2) a2 = fmaf(w2[(size_t)c * T + j], hv, a2);
+  }
+  out1[i] = a1;
+  if (out1_16) out1_16[i] = __float2bfloat16_rn(a1);
+  if (out2) {
+    out2[i] = a2;
+    if (out2_16) out2_16[i] = __float2bfloat16_rn(a2);
+  }
+}
+
+__global__ void __launch_bounds__(256) polynorm_kernel(float* __restrict__ z, const float* __restrict__ coef, float eps, int n,
+                                                       bf16* __restrict__ out16) {
+  __shared__ float red[32];
+  pdl_launch();
+  pdl_wait();
+  float* zr = z + (size_t)blockIdx.x * n;
+  float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = zr[i], v2 = v * v, v3 = v2 * v;
+    s2 += v2; s4 = fmaf(v2, v2, s4); s6 = fmaf(v3, v3, s6);
+  }
+  const float r1 = 1.0f / sqrtf(block_sum(s2, red) / (float)n + eps);
+  const float r2 = 1.0f / sqrtf(block_sum(s4, red) / (float)n + eps);
+  const float r3 = 1.0f / sqrtf(block_sum(s6, red) / (float)n + eps);
+  const float a = coef[0] * r1, b = coef[1] * r2, c = coef[2] * r3, e = coef[3];
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = zr[i], v2 = v * v;
+    const float o = fmaf(a, v, fmaf(b, v2, fmaf(c, v2 * v, e)));
+    zr[i] = o;
+    if (out16) out16[(size_t)blockIdx.x * n + i] = __float2bfloat16_rn(o);
+  }
+}
+
+__global__ void __launch_bounds__(256) parallel_combine_kernel(float* __restrict__ x, const float* __restrict__ y1,
+                                                               const float* __restrict__ y2, const float* __restrict__ ls1,
+                                                               const float* __restrict__ ls2, float* __restrict__ Xs,
+                                                               int64_t x_stride, const float* __restrict__ dwa, int n_prev,
+                                                               int64_t n, int D) {
+  pdl_launch();
+  pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int c = (int)(i % D);
+  float v = x[i];
+  v = fmaf(ls1 ? ls1[c] : 1.0f, y1[i], v);
+  if (y2) v = fmaf(ls2 ? ls2[c] : 1.0f, y2[i], v);
+  if (!Xs) { x[i] = v; return; }
+  Xs[(int64_t)n_prev * x_stride + i] = v;
+  float acc = 0.f;
+  for (int j = 0; j < n_prev; ++j) acc = fmaf(dwa[j], Xs[(int64_t)j * x_stride + i], acc);
+  x[i] = fmaf(dwa[n_prev], v, acc);
+}
+
+int row_threads(int n) { return n >= 1024 ? 256 : n >= 256 ? 128 : 64; }
+
+}  // namespace
+
+cudaError_t launch_layernorm_rows(const float* x, const float* w, float eps, int center, int rows, int D, int src_mul,
+                                  int src_add, const int32_t* src_rows, float* out, bf16* out16, cudaStream_t s) {
+  return launch_k(layernorm_rows_kernel, dim3(rows), dim3(row_threads(D)), 0, s, x, w, eps, D, center, src_mul, src_add, src_rows,
+                  out, out16);
+}
+
+cudaError_t launch_canon(const float* h, const float* tail, const float* w1, const float* w2, int B, int L, int D, int T,
+                         float* out1, bf16* out1_16, float* out2, bf16* out2_16, cudaStream_t s) {
+  const int64_t n = (int64_t)B * L * D;
+  return launch_k(canon_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, h, tail, w1, w2, L, D, T, n, out1, out1_16, out2,
+                  out2_16);
+}
+
+cudaError_t launch_polynorm(float* z, const float* coef, float eps, int rows, int n, bf16* out16, cudaStream_t s) {
+  return launch_k(polynorm_kernel, dim3(rows), dim3(row_threads(n)), 0, s, z, coef, eps, n, out16);
+}
+
+cudaError_t launch_parallel_combine(float* x, const float* y1, const float* y2, const float* ls1, const float* ls2, float* Xs,
+                                    int64_t x_stride, const float* dwa, int n_prev, int rows, int D, cudaStream_t s) {
+  const int64_t n = (int64_t)rows * D;
+  return launch_k(parallel_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, x, y1, y2, ls1, ls2, Xs, x_stride, dwa,
+                  n_prev, n, D);
+}

@@ -36,7 +36,14 @@ def _rakelorn(model_dir, config, *, dtype, max_seq_len, max_batch_size, device):
                     max_seq_len=max_seq_len or 256, max_batch_size=max_batch_size, device=device)
 
 
-ARCHITECTURES = {"Llama": _llama, "Risalix": _risalix, "Rakelorn": _rakelorn}
+def _mabedra(model_dir, config, *, dtype, max_seq_len, max_batch_size, device):
+    from .mabedra import Mabedra
+    from .utils import read_safetensors
+    return Mabedra(config, read_safetensors(os.path.join(model_dir, "model.safetensors")), dtype=dtype,
+                   max_seq_len=max_seq_len or 256, max_batch_size=max_batch_size, device=device)
+
+
+ARCHITECTURES = {"Llama": _llama, "Risalix": _risalix, "Rakelorn": _rakelorn, "Mabedra": _mabedra}
 
 
 def load_model(model_dir, *, dtype: str = "float32", max_seq_len: int = 0, max_batch_size: int = 1, device: int = 0):

@@ -18,7 +18,9 @@ import numpy as np
 from . import _cabi
 
 SOFTMAX, DECAY_LINEAR, GATED_DELTA = _cabi.MIX_SOFTMAX, _cabi.MIX_DECAY_LINEAR, _cabi.MIX_GATED_DELTA
-LATENT, MINGRU = _cabi.MIX_LATENT, _cabi.MIX_MINGRU
+LATENT, MINGRU, DIFF = _cabi.MIX_LATENT, _cabi.MIX_MINGRU, _cabi.MIX_DIFF
+FF_GLU, FF_POLYNORM = _cabi.FF_GLU, _cabi.FF_POLYNORM
+ROUTE_SOFTMAX, ROUTE_SIGMOID_IN = _cabi.ROUTE_SOFTMAX, _cabi.ROUTE_SIGMOID_IN
 _DTYPES = {"float32": _cabi.DTYPE_F32, "fp32": _cabi.DTYPE_F32, "bfloat16": _cabi.DTYPE_BF16, "bf16": _cabi.DTYPE_BF16}
 
 
@@ -46,6 +48,12 @@ class LayerSpec:
     groups: int = 1
     groups_keep: int = 1
     router_scale: float = 1.0
+    window: int = 0               # DIFF: keys a query sees, itself included; 0 = all
+    diff: float = 0.0             # DIFF: constant of lambda and of the output multiplier 1 - diff
+    rot_scaling: Optional[Tuple[float, float, float, int]] = None   # DIFF: (factor, low, high, original) or None
+    ff_kind: int = 0              # FF_GLU | FF_POLYNORM
+    router_kind: int = 0          # ROUTE_SOFTMAX | ROUTE_SIGMOID_IN
+    shared_ff: int = 0            # ROUTE_SIGMOID_IN: width of the shared expert
 
 
 @dataclass
@@ -63,6 +71,11 @@ class StackConfig:
     token_shift: bool = False     # the mixer reads its input mixed with the previous token's
     embed_scale: float = 1.0
     loop: Optional[Tuple[int, int, int]] = None   # (start, stop, times): layers [start, stop) run `times` times
+    parallel: bool = False        # one norm per layer, the mixer and the feed-forward both read it
+    norm_center: bool = False     # norms subtract the mean (layer norm with a weight, no bias)
+    layer_scale: bool = False     # per-channel multipliers l<i>.ls1 / ls2 on the sublayers' results
+    canon_taps: int = 0           # taps of the causal convolution ahead of every sublayer; 0 = none
+    depth_avg: bool = False       # the stream handed on is a weighted sum of every earlier layer's result
     max_seq_len: int = 256
     max_batch_size: int = 1
     dtype: str = "float32"
@@ -90,7 +103,13 @@ class StackDecoder:
                                          scale=l.scale, decay=C.cast(dec, C.POINTER(C.c_float)) if len(l.decay) else None,
                                          q_rank=l.q_rank, kv_rank=l.kv_rank, rot_dim=l.rot_dim, rot_dims=l.rot_dims,
                                          rot_base=float(l.rot_base), experts=l.experts, top=l.top, identity=l.identity,
-                                         groups=l.groups, groups_keep=l.groups_keep, router_scale=float(l.router_scale))
+                                         groups=l.groups, groups_keep=l.groups_keep, router_scale=float(l.router_scale),
+                                         window=l.window, diff=float(l.diff),
+                                         rot_scale_factor=float(l.rot_scaling[0]) if l.rot_scaling else 1.0,
+                                         rot_scale_low=float(l.rot_scaling[1]) if l.rot_scaling else 0.0,
+                                         rot_scale_high=float(l.rot_scaling[2]) if l.rot_scaling else 0.0,
+                                         rot_scale_original=int(l.rot_scaling[3]) if l.rot_scaling else 0,
+                                         ff_kind=l.ff_kind, router_kind=l.router_kind, shared_ff=l.shared_ff)
         c = _cabi.L3StackConfig(width=cfg.width, vocab=cfg.vocab, n_layers=len(cfg.layers), max_seq_len=cfg.max_seq_len,
                                 max_batch_size=cfg.max_batch_size, dtype=_DTYPES[cfg.dtype], device=device, flags=flags,
                                 norm_eps=cfg.norm_eps, residual_mult=cfg.residual_mult, norm_one_plus=int(cfg.norm_one_plus),
@@ -98,7 +117,9 @@ class StackDecoder:
                                 side_dim=cfg.side_dim, norm_input=int(cfg.norm_input), norm_scalar=int(cfg.norm_scalar),
                                 token_shift=int(cfg.token_shift), embed_scale=float(cfg.embed_scale),
                                 loop_start=cfg.loop[0] if cfg.loop else 0, loop_stop=cfg.loop[1] if cfg.loop else 0,
-                                loop_times=cfg.loop[2] if cfg.loop else 0)
+                                loop_times=cfg.loop[2] if cfg.loop else 0, parallel=int(cfg.parallel),
+                                norm_center=int(cfg.norm_center), layer_scale=int(cfg.layer_scale),
+                                canon_taps=int(cfg.canon_taps), depth_avg=int(cfg.depth_avg))
         _cabi.check(self._lib.l3_create_stack(C.byref(c), specs, C.byref(self._h)))
         n = C.c_int()
         _cabi.check(self._lib.l3_stack_runs(self._h, C.byref(n)), self._h)
