@@ -689,9 +689,45 @@ def rakelorn_layer_params(cfg):
     return held, read
 
 
+# ------------------------------------------------------------------------------ --arch mabedra
+# Eight parallel layers of differential sliding-window attention (two maps of 64 per head, values of 128, GQA 4:1, window
+# 1024, rotary positions with frequency scaling), convolutions of 4 taps ahead of both sublayers, layer scale, depth average;
+# feed-forward: PolyNorm dense (4 x width) in layers 0 and 4, elsewhere 16 gated experts of width / 2 (2 chosen) + a shared
+# expert of width.
+def mabedra_bench_config(width, vocab=32000):
+    heads = max(1, width // 128)
+    mixer = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 64, "vdim": 128, "diff": 0.3, "scale": 64 ** -0.5,
+             "mask": {"size": 1024},
+             "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    dense = {"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": 4 * width}}
+    moe = {"type": "attention", "mixer": mixer,
+           "mlp": {"kind": "moe", "expert": {"ff": width // 2}, "router": {"experts": 16, "top": 2}, "shared": {"ff": width}}}
+    return {"architecture": "Mabedra", "layers": [dense, moe, moe, moe, dense, moe, moe, moe], "norm": {"eps": 1e-5},
+            "canon": {"taps": 4}, "vocab": vocab, "width": width}
+
+
+def mabedra_layer_params(cfg):
+    """(parameters held, parameters a token reads: chosen experts and the shared one only)"""
+    W, held, read = cfg["width"], 0, 0
+    for lc in cfg["layers"]:
+        mc, mlp = lc["mixer"], lc["mlp"]
+        mix = W * (2 * mc["heads"] * mc["dim"] + 2 * mc["kv_heads"] * mc["dim"] + mc["kv_heads"] * mc["vdim"]) + W * mc["heads"] * mc["vdim"]
+        held += mix
+        read += mix
+        if mlp["kind"] == "dense":
+            held += 2 * W * mlp["ff"]
+            read += 2 * W * mlp["ff"]
+        else:
+            rc, ff, sh = mlp["router"], mlp["expert"]["ff"], mlp["shared"]["ff"]
+            held += rc["experts"] * W + 3 * W * (rc["experts"] * ff + sh)
+            read += rc["experts"] * W + 3 * W * (rc["top"] * ff + sh)
+    return held, read
+
+
 def run_arch_compare(a):
     import llama3_np_b200  # noqa: F401
     from llama3_np_b200 import Llama, ModelArgs, _cabi
+    from llama3_np_b200.mabedra import Mabedra
     from llama3_np_b200.rakelorn import Rakelorn
     from llama3_np_b200.risalix import Risalix
     lib = _cabi.lib()
@@ -737,6 +773,9 @@ def run_arch_compare(a):
         if a.arch == "rakelorn":
             cfg = rakelorn_bench_config(W)
             rp, rp_read = rakelorn_layer_params(cfg)
+        elif a.arch == "mabedra":
+            cfg = mabedra_bench_config(W)
+            rp, rp_read = mabedra_layer_params(cfg)
         else:
             cfg = risalix_bench_config(W)
             rp = rp_read = risalix_layer_params(cfg)
@@ -745,7 +784,7 @@ def run_arch_compare(a):
         nl = max(1, round(rp / lp1))
         clock = ClockSampler(0)
         clock.start()
-        r = (Rakelorn if a.arch == "rakelorn" else Risalix)(cfg, None, dtype=dtype, max_seq_len=M, max_batch_size=8, random_seed=1)
+        r = {"rakelorn": Rakelorn, "mabedra": Mabedra, "risalix": Risalix}[a.arch](cfg, None, dtype=dtype, max_seq_len=M, max_batch_size=8, random_seed=1)
         # the decode leg streams what a token reads (chosen experts, looped layers once per pass), the prefill leg's
         # useful work is the same count per token
         rec_r = measure(r, cfg["vocab"], rp_read + cfg["vocab"] * W, True)
@@ -774,7 +813,7 @@ def main():
     ap.add_argument("--total-len", type=int, default=256, help="profiling only: shorter generate")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="profiling only: skip the CPU legs")
     ap.add_argument("--no-extra", action="store_true", help="headline only: skip the `extra` / `tp` sub-records")
-    ap.add_argument("--arch", default="", choices=["", "risalix", "rakelorn"],
+    ap.add_argument("--arch", default="", choices=["", "risalix", "rakelorn", "mabedra"],
                     help="instead of the headline: prefill / decode throughput of this decoder family beside Llama at equal size")
     ap.add_argument("--arch-sizes", default="w1024,w2048", help="comma list of " + ",".join(ARCH_SIZES))
     ap.add_argument("--arch-prefill", type=int, default=2048)
