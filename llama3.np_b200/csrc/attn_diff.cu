@@ -99,6 +99,8 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ q, const KVT*
 }
 
 constexpr int DIFF_CTA_WARPS = 8;
+constexpr int DIFF_DEC_MAX_L = 8;     // rows per sequence the decode kernel takes
+constexpr int DIFF_DEC_CTAS = 296;    // CTAs a split decode launch aims at
 
 template <typename KVT>
 __global__ void __launch_bounds__(DIFF_CTA_WARPS * 32) attn_diff_cta_kernel(DiffAttnArgs a) {
@@ -393,6 +395,230 @@ __global__ void __launch_bounds__(256) attn_diff_tile_kernel(DiffAttnArgs a) {
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------- decode kernel
+// Few rows (L <= 8): a CTA per (key split, key head, row).  All REP query heads of the key head and both maps run against
+// the same staged work: a lane reads one key row per map ONCE and scores it for every query head, a value row read once
+// by the warp feeds all 2 REP accumulators.  Every split leaves (max, sum, o) per (head, map); attn_diff_combine_kernel
+// merges the splits, forms a1 - lambda a2 and norms the head.
+constexpr int DEC_WARPS = 4;
+
+// N = 1, 2 or 4 consecutive cache values at an N-element aligned index, as one load
+template <int N> __device__ __forceinline__ void load_vals(const float* p, float (&v)[N]) {
+  if constexpr (N == 4) { const float4 r = *reinterpret_cast<const float4*>(p); v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w; }
+  else if constexpr (N == 2) { const float2 r = *reinterpret_cast<const float2*>(p); v[0] = r.x; v[1] = r.y; }
+  else { for (int x = 0; x < N; ++x) v[x] = p[x]; }
+}
+template <int N> __device__ __forceinline__ void load_vals(const bf16* p, float (&v)[N]) {
+  if constexpr (N == 4) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xffff0000u);
+    v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xffff0000u);
+  } else if constexpr (N == 2) {
+    const uint32_t r = *reinterpret_cast<const uint32_t*>(p);
+    v[0] = __uint_as_float(r << 16); v[1] = __uint_as_float(r & 0xffff0000u);
+  } else { for (int x = 0; x < N; ++x) v[x] = __bfloat162float(p[x]); }
+}
+
+template <int DK, int DV, int REP, typename KVT>
+__global__ void __launch_bounds__(DEC_WARPS * 32) attn_diff_decode_kernel(DiffAttnArgs a, int nsplit, float* __restrict__ part_o,
+                                                                          float* __restrict__ part_ml) {
+  constexpr int NR = 2 * REP;        // (map, head) rows: index mp * REP + r
+  constexpr int VPL = DV / 32;       // value dims per lane
+  constexpr int VEC = Vec16<KVT>::N;
+  extern __shared__ __align__(16) float sm[];
+  float* qs = sm;                          // [NR][DK]
+  float* mo = qs + NR * DK;                // [DEC_WARPS][NR][DV]
+  float* mml = mo + DEC_WARPS * NR * DV;   // [DEC_WARPS][NR][2]
+  pdl_launch();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int split = blockIdx.x, g = blockIdx.y;
+  const size_t row = blockIdx.z;
+  const int b = (int)(row / a.L), t = (int)(row - (size_t)b * a.L);
+  const int last = *a.pos_ptr + t;
+  const int lo = a.window > 0 ? max(0, last - a.window + 1) : 0;
+  const int chunk = (((last - lo + 1) + nsplit - 1) / nsplit + 31) & ~31;
+  const int k_begin = lo + split * chunk, k_end = min(last, k_begin + chunk - 1);
+  for (int i = threadIdx.x; i < NR * DK; i += blockDim.x) {
+    const int mp = i / (REP * DK), rem = i - mp * (REP * DK), r = rem / DK, d = rem - r * DK;
+    qs[i] = a.q[((row * a.H + (size_t)g * REP + r) * 2 + mp) * DK + d] * a.scale;
+  }
+  __syncthreads();
+  const KVT* kb = (const KVT*)a.cache_k + ((size_t)b * 2 * a.G + 2 * g) * a.M * DK;
+  const KVT* vb = (const KVT*)a.cache_v + ((size_t)b * a.G + g) * a.M * DV;
+  float mx[NR], ls[NR], acc[NR][VPL];
+#pragma unroll
+  for (int i = 0; i < NR; ++i) {
+    mx[i] = -INFINITY; ls[i] = 0.f;
+#pragma unroll
+    for (int x = 0; x < VPL; ++x) acc[i][x] = 0.f;
+  }
+  for (int j0 = k_begin + warp * 32; j0 <= k_end; j0 += DEC_WARPS * 32) {
+    const int j = j0 + lane;
+    const bool live = j <= k_end;
+    float p[NR];
+#pragma unroll
+    for (int mp = 0; mp < 2; ++mp) {
+      float sc[REP];
+#pragma unroll
+      for (int r = 0; r < REP; ++r) sc[r] = 0.f;
+      if (live) {
+        const KVT* kr = kb + ((size_t)mp * a.M + j) * DK;
+#pragma unroll 2
+        for (int d = 0; d < DK; d += VEC) {
+          float f[VEC];
+          Vec16<KVT>::unpack(*reinterpret_cast<const uint4*>(kr + d), f);
+#pragma unroll
+          for (int r = 0; r < REP; ++r) {
+            const float* qr = qs + (mp * REP + r) * DK + d;
+#pragma unroll
+            for (int x = 0; x < VEC; x += 4) {
+              const float4 qv = *reinterpret_cast<const float4*>(qr + x);
+              sc[r] = fmaf(qv.x, f[x], sc[r]); sc[r] = fmaf(qv.y, f[x + 1], sc[r]);
+              sc[r] = fmaf(qv.z, f[x + 2], sc[r]); sc[r] = fmaf(qv.w, f[x + 3], sc[r]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < REP; ++r) {
+        const int i = mp * REP + r;
+        const float s = live ? sc[r] : -INFINITY;
+        const float mn = fmaxf(mx[i], warp_max(s));
+        const float pv = live ? expf(s - mn) : 0.f;
+        const float al = expf(mx[i] - mn);  // the warp's first batch holds its first key: mn is finite
+        ls[i] = ls[i] * al + warp_sum(pv);
+        mx[i] = mn;
+        p[i] = pv;
+#pragma unroll
+        for (int x = 0; x < VPL; ++x) acc[i][x] *= al;
+      }
+    }
+    const int nb = min(32, k_end + 1 - j0);
+    for (int u = 0; u < nb; ++u) {
+      float v[VPL];
+      load_vals<VPL>(vb + (size_t)(j0 + u) * DV + lane * VPL, v);
+#pragma unroll
+      for (int i = 0; i < NR; ++i) {
+        const float pu = __shfl_sync(L3_FULL, p[i], u);
+#pragma unroll
+        for (int x = 0; x < VPL; ++x) acc[i][x] = fmaf(pu, v[x], acc[i][x]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NR; ++i) {
+#pragma unroll
+    for (int x = 0; x < VPL; ++x) mo[((size_t)warp * NR + i) * DV + lane * VPL + x] = acc[i][x];
+    if (lane == 0) { mml[(warp * NR + i) * 2] = mx[i]; mml[(warp * NR + i) * 2 + 1] = ls[i]; }
+  }
+  __syncthreads();
+  // merge the warps (one without keys has max = -inf, sum = 0 and weighs nothing); an empty split leaves (-inf, 0, 0)
+  for (int i = warp; i < NR; i += DEC_WARPS) {
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, mml[(w * NR + i) * 2]);
+    float Lsum = 0.f, wgt[DEC_WARPS];
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      wgt[w] = M > -INFINITY ? expf(mml[(w * NR + i) * 2] - M) : 0.f;
+      Lsum = fmaf(mml[(w * NR + i) * 2 + 1], wgt[w], Lsum);
+    }
+    const int mp = i / REP, r = i - mp * REP;
+    const size_t pi = (((row * a.H + (size_t)g * REP + r) * 2 + mp) * nsplit + split);
+    for (int d = lane; d < DV; d += 32) {
+      float o = 0.f;
+#pragma unroll
+      for (int w = 0; w < DEC_WARPS; ++w) o = fmaf(mo[((size_t)w * NR + i) * DV + d], wgt[w], o);
+      part_o[pi * DV + d] = o;
+    }
+    if (lane == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = Lsum; }
+  }
+}
+
+// grid: rows * H; merges the splits of both maps of one (row, head), combines and norms
+__global__ void __launch_bounds__(128) attn_diff_combine_kernel(DiffAttnArgs a, int nsplit, const float* __restrict__ part_o,
+                                                                const float* __restrict__ part_ml) {
+  __shared__ float red[4];
+  __shared__ float wgt[2][64];
+  pdl_launch();
+  pdl_wait();
+  const size_t item = blockIdx.x;  // row * H + head
+  const int DV = a.DV, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float inv[2];
+  for (int mp = 0; mp < 2; ++mp) {
+    const float* ml = part_ml + (item * 2 + mp) * nsplit * 2;
+    float M = -INFINITY, Ls = 0.f;
+    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, ml[s * 2]);
+    for (int s = 0; s < nsplit; ++s) {
+      const float w = expf(ml[s * 2] - M);
+      Ls = fmaf(ml[s * 2 + 1], w, Ls);
+      if (threadIdx.x == 0) wgt[mp][s] = w;
+    }
+    inv[mp] = 1.0f / Ls;
+  }
+  __syncthreads();
+  const float lam = *a.lambda;
+  float ss = 0.f;
+  float keep[4];  // DV <= 512
+  int n = 0;
+  for (int d = threadIdx.x; d < DV; d += blockDim.x, ++n) {
+    float o1 = 0.f, o2 = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      o1 = fmaf(part_o[((item * 2) * nsplit + s) * DV + d], wgt[0][s], o1);
+      o2 = fmaf(part_o[((item * 2 + 1) * nsplit + s) * DV + d], wgt[1][s], o2);
+    }
+    const float o = o1 * inv[0] - lam * (o2 * inv[1]);
+    keep[n] = o;
+    ss = fmaf(o, o, ss);
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  const float tot = red[0] + red[1] + red[2] + red[3];
+  const float mul = (1.0f - a.diff) / sqrtf(tot / (float)DV + a.eps);
+  n = 0;
+  for (int d = threadIdx.x; d < DV; d += blockDim.x, ++n) {
+    const float v = keep[n] * mul;
+    a.out[item * DV + d] = v;
+    if (a.out16) a.out16[item * DV + d] = __float2bfloat16_rn(v);
+  }
+}
+
+template <int DK, int DV, int REP, typename KVT>
+cudaError_t launch_decode(const DiffAttnArgs& a, int nsplit, float* part_o, float* part_ml, cudaStream_t s) {
+  auto kern = attn_diff_decode_kernel<DK, DV, REP, KVT>;
+  constexpr size_t smem = (size_t)(2 * REP * DK + DEC_WARPS * 2 * REP * DV + DEC_WARPS * 2 * REP * 2) * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  cudaError_t e = launch_k(kern, dim3(nsplit, a.G, a.B * a.L), dim3(DEC_WARPS * 32), smem, s, a, nsplit, part_o, part_ml);
+  if (e != cudaSuccess) return e;
+  return launch_k(attn_diff_combine_kernel, dim3(a.B * a.L * a.H), dim3(128), 0, s, a, nsplit, (const float*)part_o, (const float*)part_ml);
+}
+
+template <int DK, int DV, typename KVT>
+cudaError_t launch_decode_rep(const DiffAttnArgs& a, int nsplit, float* part_o, float* part_ml, cudaStream_t s) {
+  switch (a.H / a.G) {
+    case 1: return launch_decode<DK, DV, 1, KVT>(a, nsplit, part_o, part_ml, s);
+    case 2: return launch_decode<DK, DV, 2, KVT>(a, nsplit, part_o, part_ml, s);
+    case 4: return launch_decode<DK, DV, 4, KVT>(a, nsplit, part_o, part_ml, s);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+template <typename KVT>
+cudaError_t launch_decode_t(const DiffAttnArgs& a, int nsplit, float* part_o, float* part_ml, cudaStream_t s) {
+  if (a.DK == 32 && a.DV == 32) return launch_decode_rep<32, 32, KVT>(a, nsplit, part_o, part_ml, s);
+  if (a.DK == 32 && a.DV == 64) return launch_decode_rep<32, 64, KVT>(a, nsplit, part_o, part_ml, s);
+  if (a.DK == 64 && a.DV == 64) return launch_decode_rep<64, 64, KVT>(a, nsplit, part_o, part_ml, s);
+  if (a.DK == 64 && a.DV == 128) return launch_decode_rep<64, 128, KVT>(a, nsplit, part_o, part_ml, s);
+  if (a.DK == 128 && a.DV == 128) return launch_decode_rep<128, 128, KVT>(a, nsplit, part_o, part_ml, s);
+  return cudaErrorInvalidValue;
+}
+
 template <int DK, int DV, typename KVT>
 cudaError_t launch_tile(const DiffAttnArgs& a, cudaStream_t s) {
   auto kern = attn_diff_tile_kernel<DK, DV, KVT>;
@@ -438,10 +664,21 @@ size_t diff_attn_cta_smem(int DK, int DV) {
 
 bool diff_attn_supported(int DK, int DV) { return diff_attn_cta_smem(DK, DV) <= 200 * 1024 && DK <= 12 * 1024 / 4; }
 
-cudaError_t launch_diff_attn(const DiffAttnArgs& a, bool kv_bf16, cudaStream_t s) {
-  static const int tile_min = [] { const char* v = getenv("L3_DIFF_TILE_MIN"); return v ? atoi(v) : 16; }();
+bool diff_attn_decode_shape(int DK, int DV, int rep) { return diff_attn_tiled(DK, DV) && (rep == 1 || rep == 2 || rep == 4); }
+
+size_t diff_attn_part_floats(int max_rows, int H, int DV) { return (size_t)std::max(max_rows, DIFF_DEC_CTAS) * H * 2 * DV; }
+
+cudaError_t launch_diff_attn(const DiffAttnArgs& a, bool kv_bf16, float* part_o, float* part_ml, cudaStream_t s) {
+  static const int tile_min = [] { const char* v = getenv("L3_DIFF_TILE_MIN"); return v ? atoi(v) : DIFF_DEC_MAX_L + 1; }();
+  static const bool dec_on = !(getenv("L3_DIFF_DECODE") && atoi(getenv("L3_DIFF_DECODE")) == 0);
   if (tile_min > 0 && a.L >= tile_min && diff_attn_tiled(a.DK, a.DV))
     return kv_bf16 ? launch_tile_t<bf16>(a, s) : launch_tile_t<float>(a, s);
+  if (dec_on && part_o && a.L <= DIFF_DEC_MAX_L && diff_attn_decode_shape(a.DK, a.DV, a.H / a.G)) {
+    // enough CTAs for two per SM; a split has at least 64 keys of the longest range a row can see
+    const int rows = a.B * a.L, keys = a.window > 0 ? std::min(a.window, a.M) : a.M;
+    const int nsplit = std::max(1, std::min(std::min(64, keys / 64), DIFF_DEC_CTAS / std::max(1, rows * a.G)));
+    return kv_bf16 ? launch_decode_t<bf16>(a, nsplit, part_o, part_ml, s) : launch_decode_t<float>(a, nsplit, part_o, part_ml, s);
+  }
   const size_t smem = diff_attn_cta_smem(a.DK, a.DV);
   const dim3 grid((unsigned)((size_t)a.B * a.L * a.H));
   if (kv_bf16) {

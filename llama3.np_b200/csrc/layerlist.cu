@@ -633,6 +633,13 @@ int ll_finalize(L3Model* m) {
     CK(m, cudaMalloc((void**)&ll->y1, ct * W * 4));
     CK(m, cudaMalloc((void**)&ll->y2, ct * W * 4));
     if (max_gu) CK(m, cudaMalloc((void**)&ll->moe_gu, ct * max_gu * 4));
+    size_t part = 0;
+    for (auto& L : ll->layers)
+      if (L.spec.mixer == L3_MIX_DIFF) part = std::max(part, diff_attn_part_floats(m->maxB * 8, L.spec.heads, L.spec.vdim));
+    if (part) {
+      CK(m, cudaMalloc((void**)&ll->diff_part_o, part * 4));
+      CK(m, cudaMalloc((void**)&ll->diff_part_ml, part * 4));
+    }
   }
   if (max_top) {
     CK(m, cudaMalloc((void**)&ll->moe_sel, ct * max_top * 4));
@@ -705,6 +712,7 @@ void ll_destroy(L3Model* m) {
     fr(L.canon1); fr(L.canon2); fr(L.ls1); fr(L.ls2); fr(L.dwa); fr(L.lam_vec); fr(L.lambda); fr(L.poly);
   }
   for (auto& St : ll->state) { fr(St.ck); fr(St.cv); fr(St.S); fr(St.conv_tail); fr(St.lat); fr(St.hprev); }
+  fr(ll->diff_part_o); fr(ll->diff_part_ml);
   fr(ll->Xs); fr(ll->hn); fr(ll->hf); fr(ll->hf16); fr(ll->y1); fr(ll->y2); fr(ll->moe_gu);
   fr(ll->loop_step); fr(ll->qlat); fr(ll->aux16); fr(ll->moe_sel); fr(ll->moe_w); fr(ll->moe_dense); fr(ll->moe_idw);
   fr(ll->pin); fr(ll->aux); fr(ll->rk); fr(ll->rv); fr(ll->rg); fr(ll->rbeta); fr(ll->o); fr(ll->sg); fr(ll->sg16); fr(ll->x2); fr(ll->chunk_ws);
@@ -1020,7 +1028,7 @@ static int ll_enqueue_parallel(L3Model* m, int B, int L, float* d_resid) {
     at.q = m->q; at.cache_k = St.ck; at.cache_v = St.cv; at.out = m->ctx; at.out16 = (bf16*)m->ctx16; at.lambda = Ly.lambda;
     at.pos_ptr = d_pos; at.scale = s.scale; at.diff = s.diff; at.eps = eps; at.window = s.window;
     at.B = B; at.L = L; at.H = H; at.G = G; at.DK = DK; at.DV = DV; at.M = m->M;
-    LAUNCH(m, launch_diff_attn(at, m->bf16, m->stream));
+    LAUNCH(m, launch_diff_attn(at, m->bf16, ll->diff_part_o, ll->diff_part_ml, m->stream));
     if ((rc = ll_linear(m, Ly.w_o, m->ctx, m->ctx16, 0, ntok, W, H * DV, EPI_STORE, store_to(ll->y1, nullptr, W))) != L3_OK) return rc;
     if (Ly.ff_total) {
       const int E = s.experts, ff = s.ff, F = Ly.ff_total;

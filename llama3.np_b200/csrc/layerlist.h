@@ -93,6 +93,7 @@ struct LayerList {
   void* hf16 = nullptr;
   float *y1 = nullptr, *y2 = nullptr;      // the two sublayers' results [cap_tok, width]
   float* moe_gu = nullptr;                 // [cap_tok, 2 ff_total] gate | up of every expert
+  float *diff_part_o = nullptr, *diff_part_ml = nullptr;  // split scratch of the differential decode attention
   int max_in = 0, max_o = 0, max_ff = 0;
   int head_rows = 0;  // rows the LM head's buffers hold
 };

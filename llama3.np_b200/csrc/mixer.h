@@ -181,7 +181,10 @@ struct DiffAttnArgs {
 };
 bool diff_attn_supported(int DK, int DV);
 bool diff_attn_tiled(int DK, int DV);
-cudaError_t launch_diff_attn(const DiffAttnArgs& a, bool kv_bf16, cudaStream_t s);
+// floats of split scratch (part_o; part_ml needs a DV-th of it, times 2) for calls of up to max_rows rows of <= 8 tokens per sequence
+size_t diff_attn_part_floats(int max_rows, int H, int DV);
+// part_o / part_ml: scratch of the split decode kernel (null: the decode kernel is not used)
+cudaError_t launch_diff_attn(const DiffAttnArgs& a, bool kv_bf16, float* part_o, float* part_ml, cudaStream_t s);
 
 // ---- mixture of experts (moe.cu)
 struct MoeRouteArgs {

@@ -281,7 +281,7 @@ ODD = {
                                width=36, vocab=31, taps=2),
     "one_head_one_expert": config([attn(heads=1, kv_heads=1, dim=40, vdim=72, window=1, mlp=moe(experts=1, top=1, ff=8, shared=8))], width=40, vocab=19, taps=1),
     "wide_heads": config([attn(heads=2, kv_heads=1, dim=128, vdim=128, window=50, scale=0.09, mlp=dense(ff=200))], width=72, vocab=64, eps=1e-3),
-    "tiled_64_128": config([attn(heads=2, kv_heads=2, dim=64, vdim=128, window=40, scale=0.12), attn(heads=2, kv_heads=1, dim=64, vdim=64, window=0, scale=0.12)], width=48, vocab=64),
+    "tiled_64_128": config([attn(heads=2, kv_heads=2, dim=64, vdim=128, window=40, scale=0.12), attn(heads=4, kv_heads=1, dim=64, vdim=64, window=0, scale=0.12)], width=48, vocab=64),
 }
 
 
