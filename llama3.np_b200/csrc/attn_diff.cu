@@ -33,7 +33,7 @@ __global__ void diff_lambda_kernel(const float* __restrict__ v, int n, float dif
 
 template <typename KVT>
 __global__ void __launch_bounds__(256) diff_prep_kernel(DiffPrepArgs a) {
-  extern __shared__ float sm[];  // per warp: one map's normed vector [DK]
+  extern __shared__ float sm[];  // per warp: one map's normed vector [DK]; then the row's cosines and sines [2][rot_dims / 2]
   pdl_launch();
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -43,6 +43,10 @@ __global__ void __launch_bounds__(256) diff_prep_kernel(DiffPrepArgs a) {
   const int DK = a.DK, half = a.rot_dims >> 1;
   const float* pr = a.proj + r * a.ld;
   float* vbuf = sm + (size_t)warp * DK;
+  float* cs_tab = sm + (size_t)nw * DK;
+  float* sn_tab = cs_tab + half;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * a.inv_freq[i], &sn_tab[i], &cs_tab[i]);  // every head turns by the same angles
+  __syncthreads();
   const int nq = 2 * a.H, nk = 2 * a.G;
   for (int vec = warp; vec < nq + nk; vec += nw) {
     const bool isq = vec < nq;
@@ -64,8 +68,7 @@ __global__ void __launch_bounds__(256) diff_prep_kernel(DiffPrepArgs a) {
       float o = vbuf[d];
       if (d < a.rot_dims) {
         const int i = d < half ? d : d - half;
-        float sn, cs;
-        sincosf((float)pos * a.inv_freq[i], &sn, &cs);
+        const float sn = sn_tab[i], cs = cs_tab[i];
         o = d < half ? vbuf[d] * cs - vbuf[d + half] * sn : vbuf[d] * cs + vbuf[d - half] * sn;
       }
       if (isq) qdst[d] = o;
@@ -648,7 +651,7 @@ cudaError_t launch_diff_lambda(const float* vecs, int n, float diff, float* out,
 cudaError_t launch_diff_prep(const DiffPrepArgs& a, int rows, bool kv_bf16, cudaStream_t s) {
   const int nvec = 2 * (a.H + a.G);
   const int warps = std::max(2, std::min(8, nvec));
-  const size_t smem = (size_t)warps * a.DK * sizeof(float);
+  const size_t smem = ((size_t)warps * a.DK + a.rot_dims) * sizeof(float);
   if (smem > 48 * 1024) return cudaErrorInvalidValue;
   if (kv_bf16) return launch_k(diff_prep_kernel<bf16>, dim3(rows), dim3(warps * 32), smem, s, a);
   return launch_k(diff_prep_kernel<float>, dim3(rows), dim3(warps * 32), smem, s, a);

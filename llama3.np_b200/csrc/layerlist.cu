@@ -1009,7 +1009,12 @@ static int ll_enqueue_parallel(L3Model* m, int B, int L, float* d_resid) {
     const bool has_ff = s.ff > 0;
     float *hm = m->xn, *hf = m->xn;
     bf16 *hm16 = (bf16*)m->xn16, *hf16 = (bf16*)m->xn16;  // null in fp32 mode
-    if (T > 0) {
+    // rows that go through the row-streaming GEMV need no bf16 mirror: norm, convolutions and tail in one launch
+    if (T > 0 && ntok <= 8 && norm_canon_rows_supported(L, T) && (!m->bf16 || linear_rows_supported(ntok, W))) {
+      hf = ll->hf; hf16 = (bf16*)ll->hf16;
+      LAUNCH(m, launch_norm_canon_rows(m->x, Ly.norm1, eps, ll->cfg.norm_center, St.conv_tail, Ly.canon1, has_ff ? Ly.canon2 : nullptr, B, L, W, T,
+                                       hm, has_ff ? hf : nullptr, m->stream));
+    } else if (T > 0) {
       hf = ll->hf; hf16 = (bf16*)ll->hf16;
       LAUNCH(m, launch_layernorm_rows(m->x, Ly.norm1, eps, ll->cfg.norm_center, ntok, W, 1, 0, nullptr, ll->hn, nullptr, m->stream));
       LAUNCH(m, launch_canon(ll->hn, St.conv_tail, Ly.canon1, has_ff ? Ly.canon2 : nullptr, B, L, W, T, hm, hm16, has_ff ? hf : nullptr, hf16, m->stream));

@@ -78,6 +78,111 @@ __global__ void __launch_bounds__(256) canon_kernel(const float* __restrict__ h,
   }
 }
 
+// the same for four adjacent channels per thread (D % 4 == 0): 16-byte loads and stores
+__global__ void __launch_bounds__(256) canon4_kernel(const float* __restrict__ h, const float* __restrict__ tail,
+                                                     const float* __restrict__ w1, const float* __restrict__ w2, int L, int D, int T,
+                                                     int64_t n4, float* __restrict__ out1, bf16* __restrict__ out1_16,
+                                                     float* __restrict__ out2, bf16* __restrict__ out2_16) {
+  pdl_launch();
+  pdl_wait();
+  const int64_t i4 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i4 >= n4) return;
+  const int D4 = D >> 2;
+  const int64_t r = i4 / D4;
+  const int c = (int)(i4 - r * D4) * 4;
+  const int b = (int)(r / L), t = (int)(r - (int64_t)b * L);
+  const float4 cur = *reinterpret_cast<const float4*>(h + r * D + c);
+  float a1[4] = {cur.x, cur.y, cur.z, cur.w}, a2[4] = {cur.x, cur.y, cur.z, cur.w};
+  for (int j = 0; j < T; ++j) {
+    const int v = t - (T - 1) + j;
+    float hv[4];
+    if (v >= 0) {
+      const float4 q = *reinterpret_cast<const float4*>(h + ((int64_t)b * L + v) * D + c);
+      hv[0] = q.x; hv[1] = q.y; hv[2] = q.z; hv[3] = q.w;
+    } else {
+#pragma unroll
+      for (int x = 0; x < 4; ++x) hv[x] = tail[((size_t)b * D + c + x) * (T - 1) + (T - 1 + v)];
+    }
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      a1[x] = fmaf(w1[(size_t)(c + x) * T + j], hv[x], a1[x]);
+      if (out2) a2[x] = fmaf(w2[(size_t)(c + x) * T + j], hv[x], a2[x]);
+    }
+  }
+  const int64_t o = r * D + c;
+  *reinterpret_cast<float4*>(out1 + o) = make_float4(a1[0], a1[1], a1[2], a1[3]);
+  if (out1_16) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a1[0], a1[1]), hi = __floats2bfloat162_rn(a1[2], a1[3]);
+    *reinterpret_cast<uint2*>(out1_16 + o) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+  }
+  if (out2) {
+    *reinterpret_cast<float4*>(out2 + o) = make_float4(a2[0], a2[1], a2[2], a2[3]);
+    if (out2_16) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(a2[0], a2[1]), hi = __floats2bfloat162_rn(a2[2], a2[3]);
+      *reinterpret_cast<uint2*>(out2_16 + o) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    }
+  }
+}
+
+// Few rows (L <= NORM_CANON_MAX_L tokens per sequence, T <= NORM_CANON_MAX_T taps): norm, both convolutions and the tail's
+// update in ONE launch.  A CTA per sequence: the rows' statistics first, then every thread walks its channels through the
+// call's tokens with the last T - 1 normed inputs in registers (read from the tail, written back at the end).
+constexpr int NORM_CANON_MAX_L = 8, NORM_CANON_MAX_T = 8;
+__global__ void __launch_bounds__(256) norm_canon_rows_kernel(const float* __restrict__ x, const float* __restrict__ nw, float eps,
+                                                              int center, float* __restrict__ tail, const float* __restrict__ w1,
+                                                              const float* __restrict__ w2, int L, int D, int T,
+                                                              float* __restrict__ out1, float* __restrict__ out2) {
+  __shared__ float red[32];
+  __shared__ float s_mean[NORM_CANON_MAX_L], s_rinv[NORM_CANON_MAX_L];
+  pdl_launch();
+  pdl_wait();
+  const int b = blockIdx.x;
+  const float* xb = x + (size_t)b * L * D;
+  for (int t = 0; t < L; ++t) {
+    const float* xr = xb + (size_t)t * D;
+    float mean = 0.f;
+    if (center) {
+      float s = 0.f;
+      for (int i = threadIdx.x; i < D; i += blockDim.x) s += xr[i];
+      mean = block_sum(s, red) / (float)D;
+    }
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) { const float v = xr[i] - mean; ss = fmaf(v, v, ss); }
+    const float rinv = 1.0f / sqrtf(block_sum(ss, red) / (float)D + eps);
+    if (threadIdx.x == 0) { s_mean[t] = mean; s_rinv[t] = rinv; }
+  }
+  __syncthreads();
+  const int T1 = T - 1;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    float win[NORM_CANON_MAX_T];  // win[0 .. T - 2]: the last inputs, oldest first; win[T - 1]: the current one
+    float k1[NORM_CANON_MAX_T], k2[NORM_CANON_MAX_T];
+    float* tl = tail + ((size_t)b * D + c) * T1;
+#pragma unroll
+    for (int j = 0; j < NORM_CANON_MAX_T; ++j) {
+      win[j] = j < T1 ? tl[j] : 0.f;
+      k1[j] = j < T ? w1[(size_t)c * T + j] : 0.f;
+      k2[j] = (w2 && j < T) ? w2[(size_t)c * T + j] : 0.f;
+    }
+    const float wn = nw[c];
+    for (int t = 0; t < L; ++t) {
+      const float hv = (xb[(size_t)t * D + c] - s_mean[t]) * s_rinv[t] * wn;
+      float a1 = hv, a2 = hv;
+#pragma unroll
+      for (int j = 0; j < NORM_CANON_MAX_T; ++j) {
+        if (j == T1) win[j] = hv;
+        if (j < T) { a1 = fmaf(k1[j], win[j], a1); a2 = fmaf(k2[j], win[j], a2); }
+      }
+      out1[((size_t)b * L + t) * D + c] = a1;
+      if (out2) out2[((size_t)b * L + t) * D + c] = a2;
+#pragma unroll
+      for (int j = 0; j + 1 < NORM_CANON_MAX_T; ++j) win[j] = win[j + 1];
+    }
+#pragma unroll
+    for (int j = 0; j < NORM_CANON_MAX_T; ++j)
+      if (j < T1) tl[j] = win[j];
+  }
+}
+
 __global__ void __launch_bounds__(256) polynorm_kernel(float* __restrict__ z, const float* __restrict__ coef, float eps, int n,
                                                        bf16* __restrict__ out16) {
   __shared__ float red[32];
@@ -134,8 +239,18 @@ cudaError_t launch_layernorm_rows(const float* x, const float* w, float eps, int
 cudaError_t launch_canon(const float* h, const float* tail, const float* w1, const float* w2, int B, int L, int D, int T,
                          float* out1, bf16* out1_16, float* out2, bf16* out2_16, cudaStream_t s) {
   const int64_t n = (int64_t)B * L * D;
+  if (D % 4 == 0)
+    return launch_k(canon4_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, s, h, tail, w1, w2, L, D, T, n / 4, out1, out1_16,
+                    out2, out2_16);
   return launch_k(canon_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, h, tail, w1, w2, L, D, T, n, out1, out1_16, out2,
                   out2_16);
+}
+
+bool norm_canon_rows_supported(int L, int T) { return L <= NORM_CANON_MAX_L && T >= 1 && T <= NORM_CANON_MAX_T; }
+
+cudaError_t launch_norm_canon_rows(const float* x, const float* nw, float eps, int center, float* tail, const float* w1,
+                                   const float* w2, int B, int L, int D, int T, float* out1, float* out2, cudaStream_t s) {
+  return launch_k(norm_canon_rows_kernel, dim3(B), dim3(row_threads(D)), 0, s, x, nw, eps, center, tail, w1, w2, L, D, T, out1, out2);
 }
 
 cudaError_t launch_polynorm(float* z, const float* coef, float eps, int rows, int n, bf16* out16, cudaStream_t s) {
