@@ -587,6 +587,13 @@ int ll_finalize(L3Model* m) {
   for (auto& L : ll->layers) {
     const L3LayerSpec& s = L.spec;
     const int H = s.heads, G = s.kv_heads, DK = s.dim, DV = s.vdim;
+    for (int k = 0; k < 2; ++k) {  // the convolutions' taps, tap-major for the kernels
+      float* src = k ? L.canon2 : L.canon1;
+      float** dst = k ? &L.canon2t : &L.canon1t;
+      if (!src) continue;
+      if (!*dst) CK(m, cudaMalloc((void**)dst, (size_t)m->D * ll->cfg.canon_taps * 4));
+      LAUNCH(m, launch_transpose_f32(src, m->D, ll->cfg.canon_taps, *dst, m->stream));
+    }
     if (s.mixer == L3_MIX_SOFTMAX) {
       max_rq = std::max(max_rq, H * DK);
     } else if (s.mixer == L3_MIX_DIFF) {
@@ -709,7 +716,7 @@ void ll_destroy(L3Model* m) {
     fr(L.norm1); fr(L.norm2); fr(L.side_norm); fr(L.mix_norm); fr(L.q_norm); fr(L.k_norm); fr(L.conv_w);
     fr(L.A_log); fr(L.dt_bias); fr(L.decay);
     fr(L.w_uq); fr(L.w_uk); fr(L.w_uv); fr(L.inv_freq); fr(L.in_bias); fr(L.shift); fr(L.router); fr(L.correction);
-    fr(L.canon1); fr(L.canon2); fr(L.ls1); fr(L.ls2); fr(L.dwa); fr(L.lam_vec); fr(L.lambda); fr(L.poly);
+    fr(L.canon1); fr(L.canon2); fr(L.canon1t); fr(L.canon2t); fr(L.ls1); fr(L.ls2); fr(L.dwa); fr(L.lam_vec); fr(L.lambda); fr(L.poly);
   }
   for (auto& St : ll->state) { fr(St.ck); fr(St.cv); fr(St.S); fr(St.conv_tail); fr(St.lat); fr(St.hprev); }
   fr(ll->diff_part_o); fr(ll->diff_part_ml);
@@ -1012,12 +1019,12 @@ static int ll_enqueue_parallel(L3Model* m, int B, int L, float* d_resid) {
     // rows that go through the row-streaming GEMV need no bf16 mirror: norm, convolutions and tail in one launch
     if (T > 0 && ntok <= 8 && norm_canon_rows_supported(L, T) && (!m->bf16 || linear_rows_supported(ntok, W))) {
       hf = ll->hf; hf16 = (bf16*)ll->hf16;
-      LAUNCH(m, launch_norm_canon_rows(m->x, Ly.norm1, eps, ll->cfg.norm_center, St.conv_tail, Ly.canon1, has_ff ? Ly.canon2 : nullptr, B, L, W, T,
+      LAUNCH(m, launch_norm_canon_rows(m->x, Ly.norm1, eps, ll->cfg.norm_center, St.conv_tail, Ly.canon1t, has_ff ? Ly.canon2t : nullptr, B, L, W, T,
                                        hm, has_ff ? hf : nullptr, m->stream));
     } else if (T > 0) {
       hf = ll->hf; hf16 = (bf16*)ll->hf16;
       LAUNCH(m, launch_layernorm_rows(m->x, Ly.norm1, eps, ll->cfg.norm_center, ntok, W, 1, 0, nullptr, ll->hn, nullptr, m->stream));
-      LAUNCH(m, launch_canon(ll->hn, St.conv_tail, Ly.canon1, has_ff ? Ly.canon2 : nullptr, B, L, W, T, hm, hm16, has_ff ? hf : nullptr, hf16, m->stream));
+      LAUNCH(m, launch_canon(ll->hn, St.conv_tail, Ly.canon1t, has_ff ? Ly.canon2t : nullptr, B, L, W, T, hm, hm16, has_ff ? hf : nullptr, hf16, m->stream));
       if (T > 1) LAUNCH(m, launch_conv_tail(St.conv_tail, ll->hn, W, B, L, W, T - 1, m->stream));
     } else {
       LAUNCH(m, launch_layernorm_rows(m->x, Ly.norm1, eps, ll->cfg.norm_center, ntok, W, 1, 0, nullptr, hm, hm16, m->stream));

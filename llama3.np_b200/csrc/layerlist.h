@@ -41,6 +41,7 @@ struct LLLayer {
   float* correction = nullptr;  // [experts + identity]
   // parallel layers: convolutions ahead of the sublayers [width, taps], layer scales [width], depth-average weights [layer + 2]
   float *canon1 = nullptr, *canon2 = nullptr, *ls1 = nullptr, *ls2 = nullptr, *dwa = nullptr;
+  float *canon1t = nullptr, *canon2t = nullptr;  // [taps, width] copies the kernels read (made at finalize)
   // differential attention: w_in = q | k | v rows with in_bias [n_in]; q_norm / k_norm [dim]; lam_vec = lq1 | lk1 | lq2 | lk2
   float *lam_vec = nullptr, *lambda = nullptr;
   float* poly = nullptr;        // PolyNorm coefficients (a, b, c, e); w13 is then the plain up matrix [ff, width]

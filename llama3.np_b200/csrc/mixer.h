@@ -139,7 +139,9 @@ cudaError_t launch_mingru_scan(float* proj, int ld, int z_off, int x_off, int g_
 // out[r] = (x[src] - mean) / sqrt(var + eps) * w  (center 0: x / rms * w); source rows as launch_rmsnorm_rows
 cudaError_t launch_layernorm_rows(const float* x, const float* w, float eps, int center, int rows, int D, int src_mul,
                                   int src_add, const int32_t* src_rows, float* out, bf16* out16, cudaStream_t s);
-// out_s[t] = h[t] + sum_j w_s[:, j] h[t - T + 1 + j] for s = 1, 2 (out2 null: one sublayer); h [B * L, D]; w_s [D, T];
+// dst [cols, rows] = src [rows, cols]^T (small fp32 tables at finalize)
+cudaError_t launch_transpose_f32(const float* src, int rows, int cols, float* dst, cudaStream_t s);
+// out_s[t] = h[t] + sum_j w_s[j] h[t - T + 1 + j] for s = 1, 2 (out2 null: one sublayer); h [B * L, D]; w_s [T, D] (tap-major);
 // tail [maxB, D, T - 1] holds the rows ahead of the call, oldest first (moved on by launch_conv_tail afterwards)
 cudaError_t launch_canon(const float* h, const float* tail, const float* w1, const float* w2, int B, int L, int D, int T,
                          float* out1, bf16* out1_16, float* out2, bf16* out2_16, cudaStream_t s);

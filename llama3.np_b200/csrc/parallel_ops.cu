@@ -50,7 +50,8 @@ __global__ void __launch_bounds__(256) layernorm_rows_kernel(const float* __rest
   }
 }
 
-// one thread per (row, channel); w1 / w2 [D, T], last tap = the current token; tail [maxB, D, T - 1], oldest first
+// one thread per (row, channel); w1 / w2 [T, D] (tap-major copies made at finalize), last tap = the current token;
+// tail [maxB, D, T - 1], oldest first
 __global__ void __launch_bounds__(256) canon_kernel(const float* __restrict__ h, const float* __restrict__ tail,
                                                     const float* __restrict__ w1, const float* __restrict__ w2, int L, int D, int T,
                                                     int64_t n, float* __restrict__ out1, bf16* __restrict__ out1_16,
@@ -67,8 +68,8 @@ __global__ void __launch_bounds__(256) canon_kernel(const float* __restrict__ h,
   for (int j = 0; j < T; ++j) {
     const int v = t - (T - 1) + j;  // row of this call, or (negative) a row of the tail
     const float hv = v >= 0 ? h[((int64_t)b * L + v) * D + c] : tail[((size_t)b * D + c) * (T - 1) + (T - 1 + v)];
-    a1 = fmaf(w1[(size_t)c * T + j], hv, a1);
-    if (out2) a2 = fmaf(w2[(size_t)c * T + j], hv, a2);
+    a1 = fmaf(w1[(size_t)j * D + c], hv, a1);
+    if (out2) a2 = fmaf(w2[(size_t)j * D + c], hv, a2);
   }
   out1[i] = a1;
   if (out1_16) out1_16[i] = __float2bfloat16_rn(a1);
@@ -103,10 +104,11 @@ __global__ void __launch_bounds__(256) canon4_kernel(const float* __restrict__ h
 #pragma unroll
       for (int x = 0; x < 4; ++x) hv[x] = tail[((size_t)b * D + c + x) * (T - 1) + (T - 1 + v)];
     }
-#pragma unroll
-    for (int x = 0; x < 4; ++x) {
-      a1[x] = fmaf(w1[(size_t)(c + x) * T + j], hv[x], a1[x]);
-      if (out2) a2[x] = fmaf(w2[(size_t)(c + x) * T + j], hv[x], a2[x]);
+    const float4 k1 = *reinterpret_cast<const float4*>(w1 + (size_t)j * D + c);
+    a1[0] = fmaf(k1.x, hv[0], a1[0]); a1[1] = fmaf(k1.y, hv[1], a1[1]); a1[2] = fmaf(k1.z, hv[2], a1[2]); a1[3] = fmaf(k1.w, hv[3], a1[3]);
+    if (out2) {
+      const float4 k2 = *reinterpret_cast<const float4*>(w2 + (size_t)j * D + c);
+      a2[0] = fmaf(k2.x, hv[0], a2[0]); a2[1] = fmaf(k2.y, hv[1], a2[1]); a2[2] = fmaf(k2.z, hv[2], a2[2]); a2[3] = fmaf(k2.w, hv[3], a2[3]);
     }
   }
   const int64_t o = r * D + c;
@@ -160,8 +162,8 @@ __global__ void __launch_bounds__(256) norm_canon_rows_kernel(const float* __res
 #pragma unroll
     for (int j = 0; j < NORM_CANON_MAX_T; ++j) {
       win[j] = j < T1 ? tl[j] : 0.f;
-      k1[j] = j < T ? w1[(size_t)c * T + j] : 0.f;
-      k2[j] = (w2 && j < T) ? w2[(size_t)c * T + j] : 0.f;
+      k1[j] = j < T ? w1[(size_t)j * D + c] : 0.f;
+      k2[j] = (w2 && j < T) ? w2[(size_t)j * D + c] : 0.f;
     }
     const float wn = nw[c];
     for (int t = 0; t < L; ++t) {
@@ -226,6 +228,11 @@ __global__ void __launch_bounds__(256) parallel_combine_kernel(float* __restrict
   x[i] = fmaf(dwa[n_prev], v, acc);
 }
 
+__global__ void transpose_kernel(const float* __restrict__ src, int rows, int cols, float* __restrict__ dst) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < rows * cols) dst[(size_t)(i % cols) * rows + i / cols] = src[i];
+}
+
 int row_threads(int n) { return n >= 1024 ? 256 : n >= 256 ? 128 : 64; }
 
 }  // namespace
@@ -244,6 +251,11 @@ cudaError_t launch_canon(const float* h, const float* tail, const float* w1, con
                     out2, out2_16);
   return launch_k(canon_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, h, tail, w1, w2, L, D, T, n, out1, out1_16, out2,
                   out2_16);
+}
+
+cudaError_t launch_transpose_f32(const float* src, int rows, int cols, float* dst, cudaStream_t s) {
+  transpose_kernel<<<(rows * cols + 255) / 256, 256, 0, s>>>(src, rows, cols, dst);
+  return cudaGetLastError();
 }
 
 bool norm_canon_rows_supported(int L, int T) { return L <= NORM_CANON_MAX_L && T >= 1 && T <= NORM_CANON_MAX_T; }
