@@ -180,7 +180,17 @@ struct EpiArgs {
   int L;                 // tokens per sequence in this call: row m -> (b = m / L, t = m % L)
   int HD, HN, KVHN, M;   // head_dim, local heads, local kv heads, max_seq_len
   int act;               // SWIGLU: GluAct of the gate column (0 = silu)
+  // SWIGLU with a routing weight on the unit's INPUT: output j of row m is act(w g) * (w u) with
+  // w = glu_w[m * glu_w_ld + j / glu_group] for j < glu_groups * glu_group and 1 beyond (a shared expert); w = 0 gives 0.
+  const float* glu_w;    // null: no weight
+  int glu_w_ld, glu_group, glu_groups;
 };
+// routing weight of output j (= column pair index) of row m
+__device__ __forceinline__ float glu_in_weight(const EpiArgs& e, int m, int j) {
+  if (!e.glu_w) return 1.0f;
+  const int g = j / e.glu_group;
+  return g < e.glu_groups ? e.glu_w[(size_t)m * e.glu_w_ld + g] : 1.0f;
+}
 
 template <typename KVT>
 __device__ __forceinline__ void epilogue_pair(int epi, const EpiArgs& e, int m, int col, float v0, float v1,
@@ -212,6 +222,7 @@ __device__ __forceinline__ void epilogue_pair(int epi, const EpiArgs& e, int m, 
     e.out[o] = e.resid[o] + v0;
     if (has1) e.out[o + 1] = e.resid[o + 1] + v1;
   } else if (epi == EPI_SWIGLU) {
+    if (e.glu_w) { const float w = glu_in_weight(e, m, col >> 1); v0 *= w; v1 *= w; }
     float h = glu_act(e.act, v0) * v1;
     size_t o = (size_t)m * e.ld_out + (col >> 1);
     if (e.out_lo) {

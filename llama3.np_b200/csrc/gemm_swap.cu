@@ -332,7 +332,8 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmW0, const __grid_constant
             const float up = __shfl_xor_sync(L3_FULL, v[j], 1);
             const int m = c0 + j;
             if (m < rows && n_ok && !(lane & 1)) {
-              const float h = glu_act(e.act, v[j]) * up;
+              const float w = glu_in_weight(e, m, n >> 1);
+              const float h = glu_act(e.act, v[j] * w) * (up * w);
               const size_t o = (size_t)m * e.ld_out + (n >> 1);
               if (e.out_lo) { float hh, hl; split_tf32(h, hh, hl); e.out[o] = hh; e.out_lo[o] = hl; }
               else if (e.out) e.out[o] = h;

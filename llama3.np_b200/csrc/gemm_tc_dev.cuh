@@ -500,7 +500,8 @@ __device__ __forceinline__ void tc_gemm_run(TcPipe& p, const CUtensorMap* tmA0p,
             for (int i = 0; i < 32; ++i) {
               const int m = m0 + quarter * 32 + i;
               if (m >= rows) break;
-              const float2 t = *reinterpret_cast<const float2*>(Cs + i * LDC + cp);
+              float2 t = *reinterpret_cast<const float2*>(Cs + i * LDC + cp);
+              if (e.glu_w) { const float w = glu_in_weight(e, m, col >> 1); t.x *= w; t.y *= w; }
               float hv;
               if (e.act != GLU_SILU) hv = glu_act(e.act, t.x) * t.y;
               else if constexpr (KIND == TC_BF16) hv = t.x * __fdividef(1.0f, 1.0f + __expf(-t.x)) * t.y;
