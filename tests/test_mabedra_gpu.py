@@ -190,7 +190,7 @@ def _sharp(t, n_layers, gain):
 def test_sharp_attention_over_long_contexts(window, dtype):
     """300 tokens with sharp attention: far keys (no window), windows that end on and beside a tile border of the prompt
     kernel, prompts and decoded tokens alike."""
-    cfg = config([attn(window=window, dim=32, vdim=64, scale=0.4, mlp=dense()), attn(window=window, dim=16, vdim=24)], taps=2)
+    cfg = config([attn(window=window, heads=2, kv_heads=1, dim=32, vdim=64, scale=0.4, mlp=dense()), attn(window=window, dim=16, vdim=24)], taps=2)
     t = _sharp(random_model(cfg, 17), 2, 4.0)
     m, o = build(cfg, dtype=dtype, max_seq_len=320, tensors=t)
     ids = toks(300, cfg["vocab"], seed=18)
