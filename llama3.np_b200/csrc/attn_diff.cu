@@ -7,7 +7,8 @@
 //
 //  * diff_lambda_kernel      lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff, once per layer at finalize
 //  * diff_prep_kernel        bias, RMS norm per head and map (one weight vector), rotary turn of the first rot_dims entries of
-//                            each map (entry i with entry i + rot_dims / 2) at angle position * f_i in fp32, append of the keys
+//                            each map (entry i with entry i + rot_dims / 2; the row's angles position * f_i, cosines and sines
+//                            computed once in fp32 and shared by all heads), append of the keys
 //                            [maxB, 2 G, M, DK] (head g, map m at 2 g + m) and of the biased values [maxB, G, M, DV]
 //  * attn_diff_tile_kernel   prompts: 64 queries x 64 keys per tile for one head, both maps at once - two score tiles, two
 //                            online softmaxes, two accumulators fed by the same value rows; tiles outside the window are
@@ -33,7 +34,7 @@ __global__ void diff_lambda_kernel(const float* __restrict__ v, int n, float dif
 
 template <typename KVT>
 __global__ void __launch_bounds__(256) diff_prep_kernel(DiffPrepArgs a) {
-  extern __shared__ float sm[];  // per warp: one map's normed vector [DK]; then the row's cosines and sines [2][rot_dims / 2]
+  extern __shared__ float sm[];  // the row's cosines and sines [2][rot_dims / 2]
   pdl_launch();
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -42,8 +43,7 @@ __global__ void __launch_bounds__(256) diff_prep_kernel(DiffPrepArgs a) {
   const int pos = *a.pos_ptr + t;
   const int DK = a.DK, half = a.rot_dims >> 1;
   const float* pr = a.proj + r * a.ld;
-  float* vbuf = sm + (size_t)warp * DK;
-  float* cs_tab = sm + (size_t)nw * DK;
+  float* cs_tab = sm;
   float* sn_tab = cs_tab + half;
   for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * a.inv_freq[i], &sn_tab[i], &cs_tab[i]);  // every head turns by the same angles
   __syncthreads();
@@ -51,30 +51,27 @@ __global__ void __launch_bounds__(256) diff_prep_kernel(DiffPrepArgs a) {
   for (int vec = warp; vec < nq + nk; vec += nw) {
     const bool isq = vec < nq;
     const int col = isq ? a.q_off + vec * DK : a.k_off + (vec - nq) * DK;
+    const float* src = pr + col;
+    const float* bs = a.bias + col;
     const float* w = isq ? a.wq : a.wk;
     float ss = 0.f;
-    for (int d = lane; d < DK; d += 32) {
-      const float v = pr[col + d] + a.bias[col + d];
-      vbuf[d] = v;
-      ss = fmaf(v, v, ss);
-    }
+    for (int d = lane; d < DK; d += 32) { const float v = src[d] + bs[d]; ss = fmaf(v, v, ss); }
     const float rinv = 1.0f / sqrtf(warp_sum(ss) / (float)DK + a.eps);
-    __syncwarp();
-    for (int d = lane; d < DK; d += 32) vbuf[d] = vbuf[d] * rinv * w[d];
-    __syncwarp();
     KVT* kdst = isq ? nullptr : (KVT*)a.cache_k + (((size_t)b * nk + (vec - nq)) * a.M + pos) * DK;
     float* qdst = isq ? a.q_out + r * ((size_t)nq * DK) + (size_t)vec * DK : nullptr;
-    for (int d = lane; d < DK; d += 32) {
-      float o = vbuf[d];
-      if (d < a.rot_dims) {
-        const int i = d < half ? d : d - half;
-        const float sn = sn_tab[i], cs = cs_tab[i];
-        o = d < half ? vbuf[d] * cs - vbuf[d + half] * sn : vbuf[d] * cs + vbuf[d - half] * sn;
-      }
+    // a lane holds both entries of a rotated pair (i, i + half): no exchange between lanes
+    for (int i = lane; i < half; i += 32) {
+      const float lo = (src[i] + bs[i]) * rinv * w[i], hi = (src[i + half] + bs[i + half]) * rinv * w[i + half];
+      const float sn = sn_tab[i], cs = cs_tab[i];
+      const float o_lo = lo * cs - hi * sn, o_hi = hi * cs + lo * sn;
+      if (isq) { qdst[i] = o_lo; qdst[i + half] = o_hi; }
+      else { kdst[i] = from_f32<KVT>(o_lo); kdst[i + half] = from_f32<KVT>(o_hi); }
+    }
+    for (int d = a.rot_dims + lane; d < DK; d += 32) {
+      const float o = (src[d] + bs[d]) * rinv * w[d];
       if (isq) qdst[d] = o;
       else kdst[d] = from_f32<KVT>(o);
     }
-    __syncwarp();
   }
   const int nv = a.G * a.DV;
   for (int i = threadIdx.x; i < nv; i += blockDim.x) {
@@ -651,7 +648,7 @@ cudaError_t launch_diff_lambda(const float* vecs, int n, float diff, float* out,
 cudaError_t launch_diff_prep(const DiffPrepArgs& a, int rows, bool kv_bf16, cudaStream_t s) {
   const int nvec = 2 * (a.H + a.G);
   const int warps = std::max(2, std::min(8, nvec));
-  const size_t smem = ((size_t)warps * a.DK + a.rot_dims) * sizeof(float);
+  const size_t smem = (size_t)std::max(1, a.rot_dims) * sizeof(float);
   if (smem > 48 * 1024) return cudaErrorInvalidValue;
   if (kv_bf16) return launch_k(diff_prep_kernel<bf16>, dim3(rows), dim3(warps * 32), smem, s, a);
   return launch_k(diff_prep_kernel<float>, dim3(rows), dim3(warps * 32), smem, s, a);

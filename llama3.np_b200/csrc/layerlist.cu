@@ -1008,6 +1008,10 @@ static int ll_enqueue_parallel(L3Model* m, int B, int L, float* d_resid) {
   int rc;
   ll->xcur = m->x;
   if (ll->Xs) CK(m, cudaMemcpyAsync(ll->Xs, m->x, (size_t)ntok * W * 4, cudaMemcpyDeviceToDevice, m->stream));
+  // few rows: norm, convolutions and tail are one launch, which also applies the PREVIOUS layer's combination first
+  const bool few_fused = T > 0 && ntok <= 8 && norm_canon_rows_supported(L, T) && (!m->bf16 || linear_rows_supported(ntok, W));
+  ParallelCombineArgs pre{};
+  bool have_pre = false;
   for (int ri = 0; ri < (int)ll->runs.size(); ++ri) {
     LLLayer& Ly = ll->layers[ll->runs[ri].layer];
     LLState& St = ll->state[ri];
@@ -1017,10 +1021,11 @@ static int ll_enqueue_parallel(L3Model* m, int B, int L, float* d_resid) {
     float *hm = m->xn, *hf = m->xn;
     bf16 *hm16 = (bf16*)m->xn16, *hf16 = (bf16*)m->xn16;  // null in fp32 mode
     // rows that go through the row-streaming GEMV need no bf16 mirror: norm, convolutions and tail in one launch
-    if (T > 0 && ntok <= 8 && norm_canon_rows_supported(L, T) && (!m->bf16 || linear_rows_supported(ntok, W))) {
+    if (few_fused) {
       hf = ll->hf; hf16 = (bf16*)ll->hf16;
       LAUNCH(m, launch_norm_canon_rows(m->x, Ly.norm1, eps, ll->cfg.norm_center, St.conv_tail, Ly.canon1t, has_ff ? Ly.canon2t : nullptr, B, L, W, T,
-                                       hm, has_ff ? hf : nullptr, m->stream));
+                                       hm, has_ff ? hf : nullptr, have_pre ? &pre : nullptr, m->stream));
+      have_pre = false;
     } else if (T > 0) {
       hf = ll->hf; hf16 = (bf16*)ll->hf16;
       LAUNCH(m, launch_layernorm_rows(m->x, Ly.norm1, eps, ll->cfg.norm_center, ntok, W, 1, 0, nullptr, ll->hn, nullptr, m->stream));
@@ -1078,6 +1083,12 @@ static int ll_enqueue_parallel(L3Model* m, int B, int L, float* d_resid) {
       e.act = ll->cfg.glu_act;
       if ((rc = ll_linear(m, Ly.w13, hf, hf16, 0, ntok, 2 * s.ff, W, EPI_SWIGLU, e)) != L3_OK) return rc;
       if ((rc = ll_linear(m, Ly.w2, m->h, m->h16, 0, ntok, W, s.ff, EPI_STORE, store_to(ll->y2, nullptr, W))) != L3_OK) return rc;
+    }
+    if (few_fused && !d_resid && ri + 1 < (int)ll->runs.size()) {  // left to the next layer's first launch
+      pre.y1 = ll->y1; pre.y2 = has_ff ? ll->y2 : nullptr; pre.ls1 = Ly.ls1; pre.ls2 = Ly.ls2; pre.dwa = Ly.dwa;
+      pre.Xs = ll->Xs; pre.x_stride = xs; pre.n_prev = ri + 1;
+      have_pre = true;
+      continue;
     }
     LAUNCH(m, launch_parallel_combine(m->x, ll->y1, has_ff ? ll->y2 : nullptr, Ly.ls1, Ly.ls2, ll->Xs, xs, Ly.dwa, ri + 1, ntok, W, m->stream));
     if (d_resid) CK(m, cudaMemcpyAsync(d_resid + (size_t)ri * ntok * W, m->x, (size_t)ntok * W * 4, cudaMemcpyDeviceToDevice, m->stream));

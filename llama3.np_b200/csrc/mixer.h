@@ -146,9 +146,17 @@ cudaError_t launch_transpose_f32(const float* src, int rows, int cols, float* ds
 cudaError_t launch_canon(const float* h, const float* tail, const float* w1, const float* w2, int B, int L, int D, int T,
                          float* out1, bf16* out1_16, float* out2, bf16* out2_16, cudaStream_t s);
 // few rows per sequence (norm_canon_rows_supported): launch_layernorm_rows + launch_canon + launch_conv_tail as one launch, fp32 only
+// pre (may be null): the previous layer's launch_parallel_combine, applied to x by the same launch first
+struct ParallelCombineArgs {
+  const float *y1, *y2, *ls1, *ls2, *dwa;
+  float* Xs;
+  int64_t x_stride;
+  int n_prev;
+};
 bool norm_canon_rows_supported(int L, int T);
-cudaError_t launch_norm_canon_rows(const float* x, const float* nw, float eps, int center, float* tail, const float* w1,
-                                   const float* w2, int B, int L, int D, int T, float* out1, float* out2, cudaStream_t s);
+cudaError_t launch_norm_canon_rows(float* x, const float* nw, float eps, int center, float* tail, const float* w1,
+                                   const float* w2, int B, int L, int D, int T, float* out1, float* out2,
+                                   const ParallelCombineArgs* pre, cudaStream_t s);
 // z[r] <- a N(z) + b N(z^2) + c N(z^3) + e in place (+ bf16 mirror), N = RMS norm over the n values of a row; coef = (a, b, c, e)
 cudaError_t launch_polynorm(float* z, const float* coef, float eps, int rows, int n, bf16* out16, cudaStream_t s);
 // v = x + ls1 * y1 + ls2 * y2 (y2 null: no second sublayer; ls null: ones).  Xs null: x <- v.  Else Xs[n_prev] <- v and

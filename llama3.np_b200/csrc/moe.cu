@@ -45,14 +45,52 @@ __global__ void __launch_bounds__(256) moe_route_kernel(MoeRouteArgs a) {
   __shared__ float s_score[MOE_MAX_SLOTS];   // logits, then softmax scores
   __shared__ float s_choice[MOE_MAX_SLOTS];  // score + correction; -inf once taken or out of the kept groups
   __shared__ float s_group[MOE_MAX_SLOTS];
+  __shared__ float s_part[MOE_MAX_SLOTS * 8];  // [slot][warp] partial logits
   pdl_launch();
   pdl_wait();
   const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int n = a.E + a.I, D = a.D;
   const float* h = a.h + (size_t)r * D;
-  for (int e = warp; e < n; e += nw) {
-    const float acc = warp_dot(a.router + (size_t)e * D, h, D, lane);
-    if (lane == 0) s_score[e] = acc;
+  // logits: every warp takes one slice of the input's coordinates for ALL slots (eight slots at a time, so that eight
+  // independent weight loads are in flight per input load), the slices' partial sums meet in shared memory and are added
+  // in slice order - the same arithmetic whatever the number of rows in the launch
+  const int per_w = ((D + nw - 1) / nw + 3) & ~3;
+  const int k_lo = min(D, warp * per_w), k_hi = min(D, k_lo + per_w);
+  const bool vec4 = (D % 4 == 0) && (((uintptr_t)h & 15) == 0) && (((uintptr_t)a.router & 15) == 0);
+  for (int e0 = 0; e0 < n; e0 += 8) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    if (vec4) {
+      for (int k = k_lo + lane * 4; k < k_hi; k += 128) {
+        const float4 hv = *reinterpret_cast<const float4*>(h + k);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (e0 + j < n) {
+            const float4 wv = *reinterpret_cast<const float4*>(a.router + (size_t)(e0 + j) * D + k);
+            acc[j] = fmaf(wv.x, hv.x, acc[j]); acc[j] = fmaf(wv.y, hv.y, acc[j]);
+            acc[j] = fmaf(wv.z, hv.z, acc[j]); acc[j] = fmaf(wv.w, hv.w, acc[j]);
+          }
+      }
+    } else {
+      for (int k = k_lo + lane; k < k_hi; k += 32) {
+        const float hv = h[k];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (e0 + j < n) acc[j] = fmaf(a.router[(size_t)(e0 + j) * D + k], hv, acc[j]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float t = warp_sum(acc[j]);
+      if (lane == 0 && e0 + j < n) s_part[(e0 + j) * 8 + warp] = t;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < n; e += blockDim.x) {
+    float t = 0.f;
+    for (int w = 0; w < nw; ++w) t += s_part[e * 8 + w];
+    s_score[e] = t;
   }
   __syncthreads();
   if (warp != 0) return;

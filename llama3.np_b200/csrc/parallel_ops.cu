@@ -130,16 +130,34 @@ __global__ void __launch_bounds__(256) canon4_kernel(const float* __restrict__ h
 // update in ONE launch.  A CTA per sequence: the rows' statistics first, then every thread walks its channels through the
 // call's tokens with the last T - 1 normed inputs in registers (read from the tail, written back at the end).
 constexpr int NORM_CANON_MAX_L = 8, NORM_CANON_MAX_T = 8;
-__global__ void __launch_bounds__(256) norm_canon_rows_kernel(const float* __restrict__ x, const float* __restrict__ nw, float eps,
+__global__ void __launch_bounds__(256) norm_canon_rows_kernel(float* __restrict__ x, const float* __restrict__ nw, float eps,
                                                               int center, float* __restrict__ tail, const float* __restrict__ w1,
                                                               const float* __restrict__ w2, int L, int D, int T,
-                                                              float* __restrict__ out1, float* __restrict__ out2) {
+                                                              float* __restrict__ out1, float* __restrict__ out2,
+                                                              ParallelCombineArgs pre) {
   __shared__ float red[32];
   __shared__ float s_mean[NORM_CANON_MAX_L], s_rinv[NORM_CANON_MAX_L];
   pdl_launch();
   pdl_wait();
   const int b = blockIdx.x;
-  const float* xb = x + (size_t)b * L * D;
+  float* xb = x + (size_t)b * L * D;
+  if (pre.y1) {  // the previous layer's result and the stream it hands on, for this sequence's rows (as parallel_combine_kernel)
+    for (int i = threadIdx.x; i < L * D; i += blockDim.x) {
+      const size_t gi = (size_t)b * L * D + i;
+      const int c = i % D;
+      float v = xb[i];
+      v = fmaf(pre.ls1 ? pre.ls1[c] : 1.0f, pre.y1[gi], v);
+      if (pre.y2) v = fmaf(pre.ls2 ? pre.ls2[c] : 1.0f, pre.y2[gi], v);
+      if (pre.Xs) {
+        pre.Xs[(int64_t)pre.n_prev * pre.x_stride + gi] = v;
+        float acc = 0.f;
+        for (int j = 0; j < pre.n_prev; ++j) acc = fmaf(pre.dwa[j], pre.Xs[(int64_t)j * pre.x_stride + gi], acc);
+        v = fmaf(pre.dwa[pre.n_prev], v, acc);
+      }
+      xb[i] = v;
+    }
+    __syncthreads();
+  }
   for (int t = 0; t < L; ++t) {
     const float* xr = xb + (size_t)t * D;
     float mean = 0.f;
@@ -260,9 +278,12 @@ cudaError_t launch_transpose_f32(const float* src, int rows, int cols, float* ds
 
 bool norm_canon_rows_supported(int L, int T) { return L <= NORM_CANON_MAX_L && T >= 1 && T <= NORM_CANON_MAX_T; }
 
-cudaError_t launch_norm_canon_rows(const float* x, const float* nw, float eps, int center, float* tail, const float* w1,
-                                   const float* w2, int B, int L, int D, int T, float* out1, float* out2, cudaStream_t s) {
-  return launch_k(norm_canon_rows_kernel, dim3(B), dim3(row_threads(D)), 0, s, x, nw, eps, center, tail, w1, w2, L, D, T, out1, out2);
+cudaError_t launch_norm_canon_rows(float* x, const float* nw, float eps, int center, float* tail, const float* w1,
+                                   const float* w2, int B, int L, int D, int T, float* out1, float* out2,
+                                   const ParallelCombineArgs* pre, cudaStream_t s) {
+  ParallelCombineArgs p{};
+  if (pre) p = *pre;
+  return launch_k(norm_canon_rows_kernel, dim3(B), dim3(row_threads(D)), 0, s, x, nw, eps, center, tail, w1, w2, L, D, T, out1, out2, p);
 }
 
 cudaError_t launch_polynorm(float* z, const float* coef, float eps, int rows, int n, bf16* out16, cudaStream_t s) {
