@@ -9,6 +9,8 @@
 //  * polynorm_kernel          a N(z) + b N(z^2) + c N(z^3) + e over a token's feed-forward values, N = RMS norm
 //  * parallel_combine_kernel  X_new = x + ls1 * y1 + ls2 * y2, stored as layer result i + 1, and the stream handed on:
 //                             x = sum_j dwa[j] X_j over the embedding output and every layer result so far
+#include <algorithm>
+
 #include "common.cuh"
 #include "mixer.h"
 
@@ -130,7 +132,7 @@ __global__ void __launch_bounds__(256) canon4_kernel(const float* __restrict__ h
 // update in ONE launch.  A CTA per sequence: the rows' statistics first, then every thread walks its channels through the
 // call's tokens with the last T - 1 normed inputs in registers (read from the tail, written back at the end).
 constexpr int NORM_CANON_MAX_L = 8, NORM_CANON_MAX_T = 8;
-__global__ void __launch_bounds__(256) norm_canon_rows_kernel(float* __restrict__ x, const float* __restrict__ nw, float eps,
+__global__ void __launch_bounds__(1024) norm_canon_rows_kernel(float* __restrict__ x, const float* __restrict__ nw, float eps,
                                                               int center, float* __restrict__ tail, const float* __restrict__ w1,
                                                               const float* __restrict__ w2, int L, int D, int T,
                                                               float* __restrict__ out1, float* __restrict__ out2,
@@ -203,7 +205,7 @@ __global__ void __launch_bounds__(256) norm_canon_rows_kernel(float* __restrict_
   }
 }
 
-__global__ void __launch_bounds__(256) polynorm_kernel(float* __restrict__ z, const float* __restrict__ coef, float eps, int n,
+__global__ void __launch_bounds__(1024) polynorm_kernel(float* __restrict__ z, const float* __restrict__ coef, float eps, int n,
                                                        bf16* __restrict__ out16) {
   __shared__ float red[32];
   pdl_launch();
@@ -252,6 +254,8 @@ __global__ void transpose_kernel(const float* __restrict__ src, int rows, int co
 }
 
 int row_threads(int n) { return n >= 1024 ? 256 : n >= 256 ? 128 : 64; }
+// a launch of a few CTAs only (decode): as many threads as the row has pairs of entries, up to 1024
+int few_row_threads(int n) { return std::min(1024, std::max(64, (n / 2 + 31) & ~31)); }
 
 }  // namespace
 
@@ -283,11 +287,11 @@ cudaError_t launch_norm_canon_rows(float* x, const float* nw, float eps, int cen
                                    const ParallelCombineArgs* pre, cudaStream_t s) {
   ParallelCombineArgs p{};
   if (pre) p = *pre;
-  return launch_k(norm_canon_rows_kernel, dim3(B), dim3(row_threads(D)), 0, s, x, nw, eps, center, tail, w1, w2, L, D, T, out1, out2, p);
+  return launch_k(norm_canon_rows_kernel, dim3(B), dim3(few_row_threads(D)), 0, s, x, nw, eps, center, tail, w1, w2, L, D, T, out1, out2, p);
 }
 
 cudaError_t launch_polynorm(float* z, const float* coef, float eps, int rows, int n, bf16* out16, cudaStream_t s) {
-  return launch_k(polynorm_kernel, dim3(rows), dim3(row_threads(n)), 0, s, z, coef, eps, n, out16);
+  return launch_k(polynorm_kernel, dim3(rows), dim3(rows <= 8 ? few_row_threads(n) : row_threads(n)), 0, s, z, coef, eps, n, out16);
 }
 
 cudaError_t launch_parallel_combine(float* x, const float* y1, const float* y2, const float* ls1, const float* ls2, float* Xs,
