@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(256) diff_prep_kernel(DiffPrepArgs a) {
   for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * a.inv_freq[i], &sn_tab[i], &cs_tab[i]);  // every head turns by the same angles
   __syncthreads();
   const int nq = 2 * a.H, nk = 2 * a.G;
-  for (int vec = warp; vec < nq + nk; vec += nw) {
+  for (int vec = blockIdx.y * nw + warp; vec < nq + nk; vec += gridDim.y * nw) {  // a row's vectors spread over gridDim.y CTAs
     const bool isq = vec < nq;
     const int col = isq ? a.q_off + vec * DK : a.k_off + (vec - nq) * DK;
     const float* src = pr + col;
@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(256) diff_prep_kernel(DiffPrepArgs a) {
     }
   }
   const int nv = a.G * a.DV;
-  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < nv; i += gridDim.y * blockDim.x) {
     const int g = i / a.DV, d = i - g * a.DV;
     ((KVT*)a.cache_v)[(((size_t)b * a.G + g) * a.M + pos) * a.DV + d] = from_f32<KVT>(pr[a.v_off + i] + a.bias[a.v_off + i]);
   }
@@ -650,8 +650,9 @@ cudaError_t launch_diff_prep(const DiffPrepArgs& a, int rows, bool kv_bf16, cuda
   const int warps = std::max(2, std::min(8, nvec));
   const size_t smem = (size_t)std::max(1, a.rot_dims) * sizeof(float);
   if (smem > 48 * 1024) return cudaErrorInvalidValue;
-  if (kv_bf16) return launch_k(diff_prep_kernel<bf16>, dim3(rows), dim3(warps * 32), smem, s, a);
-  return launch_k(diff_prep_kernel<float>, dim3(rows), dim3(warps * 32), smem, s, a);
+  const dim3 grid(rows, (nvec + warps - 1) / warps);
+  if (kv_bf16) return launch_k(diff_prep_kernel<bf16>, grid, dim3(warps * 32), smem, s, a);
+  return launch_k(diff_prep_kernel<float>, grid, dim3(warps * 32), smem, s, a);
 }
 
 bool diff_attn_tiled(int DK, int DV) {
