@@ -209,9 +209,12 @@ constexpr size_t diff_tile_smem() {
   return (size_t)(2 * DT_ROWS * (DK + 4) + 2 * DT_TK * (DK + 4) + DT_TK * DV + 2 * DT_ROWS * DT_LDS + 6 * DT_ROWS) * sizeof(float);
 }
 
-template <int DK, int DV, typename KVT>
-__global__ void __launch_bounds__(256) attn_diff_tile_kernel(DiffAttnArgs a) {
-  constexpr int LDK = DK + 4, DK4 = DK / 4, DV4 = DV / 4, NCH = (DV + 63) / 64;
+// TXN lanes share a group of four queries: 16 (256 threads, four keys and 4 x DV / 64 output columns per thread) or, for values
+// of 128 and more, 32 (512 threads, two keys per thread; a warp then reads ONE query row - a broadcast - per load)
+template <int DK, int DV, int TXN, typename KVT>
+__global__ void __launch_bounds__(16 * TXN) attn_diff_tile_kernel(DiffAttnArgs a) {
+  constexpr int NT = 16 * TXN, KPT = DT_TK / TXN, NWARP = NT / 32, RPW = 2 * DT_ROWS / NWARP;
+  constexpr int LDK = DK + 4, DK4 = DK / 4, DV4 = DV / 4, NCH = (DV + 4 * TXN - 1) / (4 * TXN);
   extern __shared__ __align__(16) float sm[];
   float* Qs = sm;                           // [2][ROWS][LDK]
   float* Ks = Qs + 2 * DT_ROWS * LDK;       // [2][TK][LDK]
@@ -219,7 +222,7 @@ __global__ void __launch_bounds__(256) attn_diff_tile_kernel(DiffAttnArgs a) {
   float* Ss = Vs + DT_TK * DV;              // [2][ROWS][LDS]
   float* St = Ss + 2 * DT_ROWS * DT_LDS;    // [2][ROWS][3]: running max, running sum, rescale of this tile
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int ty = tid >> 4, tx = tid & 15;
+  const int ty = tid / TXN, tx = tid % TXN;
   const int head = blockIdx.y, b = blockIdx.z;
   const int g = head / (a.H / a.G);
   pdl_launch();
@@ -229,14 +232,14 @@ __global__ void __launch_bounds__(256) attn_diff_tile_kernel(DiffAttnArgs a) {
   const int nq = min(DT_ROWS, a.L - q0);
   const int t_hi = start + q0 + nq;  // one past the last visible key
   const int k_lo = a.window > 0 ? max(0, start + q0 - a.window + 1) : 0;
-  for (int i = tid; i < 2 * DT_ROWS * DK4; i += 256) {
+  for (int i = tid; i < 2 * DT_ROWS * DK4; i += NT) {
     const int mp = i / (DT_ROWS * DK4), rem = i - mp * (DT_ROWS * DK4);
     const int r = rem / DK4, d4 = rem - r * DK4;
     float4 v = make_float4(0, 0, 0, 0);
     if (r < nq) v = *reinterpret_cast<const float4*>(a.q + (((size_t)b * a.L + q0 + r) * a.H + head) * (2 * DK) + mp * DK + d4 * 4);
     *reinterpret_cast<float4*>(Qs + (mp * DT_ROWS + r) * LDK + d4 * 4) = v;
   }
-  for (int i = tid; i < 2 * DT_ROWS; i += 256) { St[i * 3] = -INFINITY; St[i * 3 + 1] = 0.f; St[i * 3 + 2] = 1.f; }
+  for (int i = tid; i < 2 * DT_ROWS; i += NT) { St[i * 3] = -INFINITY; St[i * 3 + 1] = 0.f; St[i * 3 + 2] = 1.f; }
   float4 acc[2][4][NCH];
 #pragma unroll
   for (int mp = 0; mp < 2; ++mp)
@@ -249,7 +252,7 @@ __global__ void __launch_bounds__(256) attn_diff_tile_kernel(DiffAttnArgs a) {
 
   for (int k0 = k_lo; k0 < t_hi; k0 += DT_TK) {
     __syncthreads();
-    for (int i = tid; i < 2 * DT_TK * DK4; i += 256) {
+    for (int i = tid; i < 2 * DT_TK * DK4; i += NT) {
       const int mp = i / (DT_TK * DK4), rem = i - mp * (DT_TK * DK4);
       const int key = rem / DK4, d4 = rem - key * DK4;
       const int t = k0 + key;
@@ -257,7 +260,7 @@ __global__ void __launch_bounds__(256) attn_diff_tile_kernel(DiffAttnArgs a) {
       if (t < t_hi) kv = ld_kv4<KVT>(kbase + ((size_t)mp * a.M + t) * DK + d4 * 4);
       *reinterpret_cast<float4*>(Ks + (mp * DT_TK + key) * LDK + d4 * 4) = kv;
     }
-    for (int i = tid; i < DT_TK * DV4; i += 256) {
+    for (int i = tid; i < DT_TK * DV4; i += NT) {
       const int key = i / DV4, d4 = i - key * DV4;
       const int t = k0 + key;
       float4 vv = make_float4(0, 0, 0, 0);
@@ -266,25 +269,25 @@ __global__ void __launch_bounds__(256) attn_diff_tile_kernel(DiffAttnArgs a) {
     }
     __syncthreads();
 #pragma unroll
-    for (int mp = 0; mp < 2; ++mp) {  // scores of both maps: queries ty * 4 + i, keys tx + 16 j
-      float s[4][4];
+    for (int mp = 0; mp < 2; ++mp) {  // scores of both maps: queries ty * 4 + i, keys tx + TXN j
+      float s[4][KPT];
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+        for (int j = 0; j < KPT; ++j) s[i][j] = 0.f;
       const float* Qm = Qs + mp * DT_ROWS * LDK;
       const float* Km = Ks + mp * DT_TK * LDK;
 #pragma unroll 2
       for (int d4 = 0; d4 < DK4; ++d4) {
-        float4 qv[4], kv[4];
+        float4 qv[4], kv[KPT];
 #pragma unroll
         for (int i = 0; i < 4; ++i) qv[i] = *reinterpret_cast<const float4*>(Qm + (ty * 4 + i) * LDK + d4 * 4);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) kv[j] = *reinterpret_cast<const float4*>(Km + (tx + 16 * j) * LDK + d4 * 4);
+        for (int j = 0; j < KPT; ++j) kv[j] = *reinterpret_cast<const float4*>(Km + (tx + TXN * j) * LDK + d4 * 4);
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < KPT; ++j) {
             s[i][j] = fmaf(qv[i].x, kv[j].x, s[i][j]); s[i][j] = fmaf(qv[i].y, kv[j].y, s[i][j]);
             s[i][j] = fmaf(qv[i].z, kv[j].z, s[i][j]); s[i][j] = fmaf(qv[i].w, kv[j].w, s[i][j]);
           }
@@ -294,16 +297,16 @@ __global__ void __launch_bounds__(256) attn_diff_tile_kernel(DiffAttnArgs a) {
         const int r = ty * 4 + i;
         const int qpos = start + q0 + r;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int key = tx + 16 * j, kp = k0 + key;
+        for (int j = 0; j < KPT; ++j) {
+          const int key = tx + TXN * j, kp = k0 + key;
           const bool vis = r < nq && kp <= qpos && (a.window <= 0 || qpos - kp < a.window);
           Ss[(mp * DT_ROWS + r) * DT_LDS + key] = vis ? s[i][j] * a.scale : -INFINITY;
         }
       }
     }
     __syncthreads();
-    for (int rr = 0; rr < 16; ++rr) {  // online softmax: warp w owns rows 16 w .. 16 w + 15 of the 128 (map, query) rows
-      const int r = warp * 16 + rr;
+    for (int rr = 0; rr < RPW; ++rr) {  // online softmax: every warp owns RPW of the 128 (map, query) rows
+      const int r = warp * RPW + rr;
       float* srow = Ss + r * DT_LDS;
       const float mold = St[r * 3];
       const float s0 = srow[lane], s1 = srow[lane + 32];
@@ -338,7 +341,7 @@ __global__ void __launch_bounds__(256) attn_diff_tile_kernel(DiffAttnArgs a) {
           for (int i = 0; i < 4; ++i) p[mp][i] = *reinterpret_cast<const float4*>(Ss + (mp * DT_ROWS + ty * 4 + i) * DT_LDS + k4 * 4);
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
-          const int d = tx * 4 + 64 * c;
+          const int d = tx * 4 + 4 * TXN * c;
           if (d < DV) {
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
@@ -369,16 +372,16 @@ __global__ void __launch_bounds__(256) attn_diff_tile_kernel(DiffAttnArgs a) {
       float4& o = acc[0][i][c];
       const float4 o2 = acc[1][i][c];
       o.x = o.x * i1 - o2.x * i2; o.y = o.y * i1 - o2.y * i2; o.z = o.z * i1 - o2.z * i2; o.w = o.w * i1 - o2.w * i2;
-      if (tx * 4 + 64 * c < DV) ss += o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w;
+      if (tx * 4 + 4 * TXN * c < DV) ss += o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w;
     }
-    // the 16 threads of a query row are 16 adjacent lanes
+    // the TXN threads of a query row are adjacent lanes
 #pragma unroll
-    for (int off = 8; off > 0; off >>= 1) ss += __shfl_xor_sync(L3_FULL, ss, off);
+    for (int off = TXN / 2; off > 0; off >>= 1) ss += __shfl_xor_sync(L3_FULL, ss, off);
     const float mul = (1.0f - a.diff) / sqrtf(ss / (float)DV + a.eps);
     if (r >= nq) continue;
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
-      const int d = tx * 4 + 64 * c;
+      const int d = tx * 4 + 4 * TXN * c;
       if (d >= DV) continue;
       float4 o = acc[0][i][c];
       o.x *= mul; o.y *= mul; o.z *= mul; o.w *= mul;
@@ -621,11 +624,12 @@ cudaError_t launch_decode_t(const DiffAttnArgs& a, int nsplit, float* part_o, fl
 
 template <int DK, int DV, typename KVT>
 cudaError_t launch_tile(const DiffAttnArgs& a, cudaStream_t s) {
-  auto kern = attn_diff_tile_kernel<DK, DV, KVT>;
+  constexpr int TXN = DV >= 128 ? 32 : 16;
+  auto kern = attn_diff_tile_kernel<DK, DV, TXN, KVT>;
   constexpr size_t smem = diff_tile_smem<DK, DV>();
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  return launch_k(kern, dim3((a.L + DT_ROWS - 1) / DT_ROWS, a.H, a.B), dim3(256), smem, s, a);
+  return launch_k(kern, dim3((a.L + DT_ROWS - 1) / DT_ROWS, a.H, a.B), dim3(16 * TXN), smem, s, a);
 }
 
 template <typename KVT>
