@@ -468,7 +468,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_diff_decode_kernel(DiffAt
       for (int r = 0; r < REP; ++r) sc[r] = 0.f;
       if (live) {
         const KVT* kr = kb + ((size_t)mp * a.M + j) * DK;
-#pragma unroll 2
+#pragma unroll 4
         for (int d = 0; d < DK; d += VEC) {
           float f[VEC];
           Vec16<KVT>::unpack(*reinterpret_cast<const uint4*>(kr + d), f);
@@ -498,16 +498,20 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_diff_decode_kernel(DiffAt
         for (int x = 0; x < VPL; ++x) acc[i][x] *= al;
       }
     }
+    // eight value rows in flight at a time; rows past the split's end are read clamped and weigh nothing (their p is 0)
     const int nb = min(32, k_end + 1 - j0);
-    for (int u = 0; u < nb; ++u) {
-      float v[VPL];
-      load_vals<VPL>(vb + (size_t)(j0 + u) * DV + lane * VPL, v);
+    for (int u0 = 0; u0 < nb; u0 += 8) {
+      float v[8][VPL];
 #pragma unroll
-      for (int i = 0; i < NR; ++i) {
-        const float pu = __shfl_sync(L3_FULL, p[i], u);
+      for (int u = 0; u < 8; ++u) load_vals<VPL>(vb + (size_t)min(j0 + u0 + u, k_end) * DV + lane * VPL, v[u]);
 #pragma unroll
-        for (int x = 0; x < VPL; ++x) acc[i][x] = fmaf(pu, v[x], acc[i][x]);
-      }
+      for (int u = 0; u < 8; ++u)
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+          const float pu = __shfl_sync(L3_FULL, p[i], u0 + u);
+#pragma unroll
+          for (int x = 0; x < VPL; ++x) acc[i][x] = fmaf(pu, v[u][x], acc[i][x]);
+        }
     }
   }
 #pragma unroll
