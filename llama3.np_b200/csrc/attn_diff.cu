@@ -658,7 +658,7 @@ cudaError_t launch_diff_prep(const DiffPrepArgs& a, int rows, bool kv_bf16, cuda
   const int warps = std::max(2, std::min(8, nvec));
   const size_t smem = (size_t)std::max(1, a.rot_dims) * sizeof(float);
   if (smem > 48 * 1024) return cudaErrorInvalidValue;
-  const dim3 grid(rows, (nvec + warps - 1) / warps);
+  const dim3 grid(rows, rows <= 64 ? (nvec + warps - 1) / warps : 1);  // few rows: a row's vectors spread over several CTAs
   if (kv_bf16) return launch_k(diff_prep_kernel<bf16>, grid, dim3(warps * 32), smem, s, a);
   return launch_k(diff_prep_kernel<float>, grid, dim3(warps * 32), smem, s, a);
 }
