@@ -26,6 +26,14 @@
 //   and a feed-forward that is a mixture of experts (moe.cu): fp32 router -> few rows: only the chosen experts' weights
 //   are read; many rows: ONE up-projection over all experts, relu^2 times the routing weight (zero where not chosen),
 //   ONE down-projection whose K runs over all experts and so sums them.
+// Parallel stacks (L3StackConfig::parallel, ll_enqueue_parallel):  h = norm1(x);  X_new = x + ls1 mixer(h + conv1(h)) +
+// ls2 ff(h + conv2(h));  x <- sum_j dwa[j] X_j over the embedding output and every layer result so far.  One mixer:
+//
+//   differential  fused q|k|v projection -> biases, RMS norm per head and map, rotary turn, append of both maps' keys and of
+//                 the values (attn_diff.cu) -> two softmax maps per head over a sliding window of the same values, combined
+//                 as a1 - lambda a2 and normed per head
+//   and a feed-forward that is dense with the PolyNorm activation (parallel_ops.cu) or a mixture of gated experts routed by
+//   sigmoid scores whose weights scale the experts' input, with a shared expert (moe.cu), or none.
 // A block of layers can run several times per token (loop_*): the execution order is a list of layer RUNS, every run
 // with its own cache / state (LLState); the pass's step vector is added ahead of the block's first layer.
 //

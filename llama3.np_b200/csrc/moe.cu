@@ -1,6 +1,7 @@
 // Mixture-of-experts feed-forward of layer-list decoders (layerlist.cu).
 //
-//  * moe_route_kernel      one CTA per token: fp32 router logits over experts + identity slots, softmax, the choice
+//  * moe_route_kernel      one CTA per token: fp32 router logits over experts + identity slots (a warp per slice of the
+//                          input's coordinates, eight slots at a time, slices summed in a fixed order), softmax, the choice
 //                          scores (score + correction), group limitation (only slots of the `keep` groups with the
 //                          largest best choice score stay eligible), the `top` largest choices (ties: lower slot),
 //                          weights = scale * score.  Emits the chosen slots and weights, the dense [rows, E] weight
@@ -10,6 +11,11 @@
 //                          experts the row did not choose - and one GEMM over K = experts * ff sums the experts.
 //  * moe_up_rows / moe_down_rows   few rows (decode): a warp per output reads only the chosen experts' rows.
 //  * moe_identity_kernel   x += (weight of the chosen identity slots) * h
+//  Router kind 1 (sigmoid scores, the largest win, weight = score, applied to the expert's INPUT) with gated experts
+//  down(silu(w g) * (w u)) and a shared expert:
+//  * moe_glu_act_kernel    masked-dense path: [rows, 2 F] interleaved (gate, up) of all experts and the shared one ->
+//                          [rows, F] hidden values, zero where the row did not choose the expert
+//  * moe_glu_up_rows / moe_glu_down_rows   few rows: only the chosen experts' and the shared expert's rows are read
 #include "common.cuh"
 #include "mixer.h"
 

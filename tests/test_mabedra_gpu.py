@@ -396,3 +396,48 @@ def test_larger_shapes_take_the_tensor_core_projections():
                               np.stack([m.forward(ids[None, i:i + 1], i)[0] for i in range(150, 160)])])
         assert close(got, want, dtype)
         m.close()
+
+
+@pytest.mark.parametrize("seed", [101, 102, 103, 104])
+def test_random_configurations(seed):
+    """Configurations drawn at random - widths, vocabularies, taps, layer counts and orders, head counts and sizes, rotated
+    parts, windows, constants, feed-forward kinds - each as a whole prompt, as a prompt with decoded tokens and in random
+    portions, in both modes."""
+    rng = np.random.default_rng(seed)
+    for _ in range(5):
+        layers = []
+        for _ in range(int(rng.integers(1, 5))):
+            G, rep = int(rng.choice([1, 2, 3])), int(rng.choice([1, 2, 4]))
+            dim, vdim = int(rng.choice([8, 16, 24, 32, 64])), int(rng.choice([8, 16, 32, 40, 64, 128]))
+            k = rng.random()
+            if k < 0.2:
+                mlp = None
+            elif k < 0.5:
+                mlp = dense(int(rng.choice([40, 64, 100])))
+            else:
+                E = int(rng.choice([1, 3, 4, 9]))
+                mlp = moe(experts=E, top=int(rng.integers(1, min(E, 3) + 1)), ff=int(rng.choice([8, 24, 48])), shared=int(rng.choice([0, 16, 40])))
+            layers.append(attn(heads=G * rep, kv_heads=G, dim=dim, vdim=vdim, window=int(rng.choice([0, 1, 5, 31, 64, 90])),
+                               diff=float(rng.choice([0.1, 0.4, 0.7])), scale=float(dim ** -0.5 * rng.choice([0.5, 1.0, 2.0])),
+                               base=float(rng.choice([50.0, 10000.0, 300000.0])), dims=int(rng.choice([dim, dim // 2, dim // 4 * 2, 0])),
+                               scaling=None if rng.random() < 0.3 else (float(rng.choice([2.0, 8.0])), 1.0, float(rng.choice([2.0, 4.0])), int(rng.choice([16, 128]))),
+                               mlp=mlp))
+        cfg = config(layers, width=int(rng.choice([24, 40, 64, 100, 128])), vocab=int(rng.choice([50, 97, 300])),
+                     taps=int(rng.choice([0, 1, 2, 4, 7])), eps=float(rng.choice([1e-6, 1e-5, 1e-3])))
+        n = int(rng.choice([30, 75, 140]))
+        t = random_model(cfg, int(rng.integers(1 << 30)))
+        ids = rng.integers(0, cfg["vocab"], n)
+        want = OracleMabedra(cfg, t).run(ids)
+        for dtype in ("float32", "bfloat16"):
+            m, _ = build(cfg, dtype=dtype, max_seq_len=n + 4, tensors=t)
+            assert close(m.forward_rows(ids[None], 0, list(range(n))), want, dtype), (dtype, cfg)
+            nd = min(n - 1, 20)
+            got = np.concatenate([m.forward_rows(ids[None, :n - nd], 0, list(range(n - nd)))] + [m.forward(ids[None, i:i + 1], i) for i in range(n - nd, n)])
+            assert close(got, want, dtype), (dtype, cfg)
+            rows, pos = [], 0
+            while pos < n:
+                c = int(min(n - pos, rng.choice([1, 2, 2, 3, 7, 16, 33, 64])))
+                rows.append(m.forward_rows(ids[None, pos:pos + c], pos, list(range(c))))
+                pos += c
+            assert close(np.concatenate(rows), want, dtype), (dtype, cfg)
+            m.close()
