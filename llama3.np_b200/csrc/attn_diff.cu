@@ -683,9 +683,9 @@ cudaError_t launch_diff_attn(const DiffAttnArgs& a, bool kv_bf16, float* part_o,
   if (tile_min > 0 && a.L >= tile_min && diff_attn_tiled(a.DK, a.DV))
     return kv_bf16 ? launch_tile_t<bf16>(a, s) : launch_tile_t<float>(a, s);
   if (dec_on && part_o && a.L <= DIFF_DEC_MAX_L && diff_attn_decode_shape(a.DK, a.DV, a.H / a.G)) {
-    // enough CTAs for two per SM; a split has at least 64 keys of the longest range a row can see
+    // enough CTAs for two per SM; a split has at least 128 keys of the longest range a row can see (a batch of 32 per warp)
     const int rows = a.B * a.L, keys = a.window > 0 ? std::min(a.window, a.M) : a.M;
-    const int nsplit = std::max(1, std::min(std::min(64, keys / 64), DIFF_DEC_CTAS / std::max(1, rows * a.G)));
+    const int nsplit = std::max(1, std::min(std::min(64, keys / (DEC_WARPS * 32)), DIFF_DEC_CTAS / std::max(1, rows * a.G)));
     return kv_bf16 ? launch_decode_t<bf16>(a, nsplit, part_o, part_ml, s) : launch_decode_t<float>(a, nsplit, part_o, part_ml, s);
   }
   const size_t smem = diff_attn_cta_smem(a.DK, a.DV);
