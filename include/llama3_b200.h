@@ -160,6 +160,25 @@ int l3_generate_ragged(L3Model* m, const int32_t* ids, const int32_t* lens, int 
                                   i + rot_dims / 2, frequencies rot_base^(-2 i / rot_dims) rescaled by wavelength
                                   (rot_scale_*); query i sees keys j with 0 <= i - j < window (window 0: every earlier key).
                                   Built for parallel layers (L3StackConfig::parallel)                                     */
+#define L3_MIX_WINDOW 6        /* sliding-window attention, GQA, key size dim and value size vdim: query i sees key j <= i with
+                                  i - j < window (window 0: every earlier key) or j < keep_first (the first tokens stay visible at
+                                  their true positions); rotary positions on the first rot_dims entries of every head, pairs
+                                  (2i, 2i + 1) (rot_layout 0) or (i, i + rot_dims / 2) (rot_layout 1), frequencies
+                                  rot_base^(-2 i / rot_dims); qk_unit 1: q and k are divided by their root mean square per head
+                                  after the rotation (no weight); score = q . k * scale; attn_kind L3_ATTN_SINK: softmax whose
+                                  denominator also holds exp(sink_h) (tensor mix.sink [heads]), L3_ATTN_SIGMOID: the weight of a
+                                  visible key is sigmoid(score + pb_h) (tensor mix.pb [heads]), not normalised over keys       */
+#define L3_MIX_SSD 7           /* Mamba-2 state-space mixer: one projection laid out [z | x | B | C | dt] (heads * vdim twice,
+                                  kv_heads * dim twice, heads); x | B | C pass a causal convolution of conv_taps taps with bias
+                                  and silu; dt <- softplus(dt + dt_bias); per head S <- exp(-exp(A_log) dt) S + dt B x^T
+                                  (S is dim x vdim, dim = the state size, kv_heads = the B / C groups), y = S^T C + D x; then
+                                  y * silu(z), an RMS norm in out_norm_groups equal parts with weight mix.norm, mix.o           */
+#define L3_MIX_GLA 8           /* gated linear attention: q dim^(-1/2), k (heads x dim), v (heads x vdim); a decay per key channel
+                                  alpha = sigmoid(a2 (a1 h) + a2.b)^(1 / tau); S <- diag(alpha) S + k v^T, o = S^T q; RMS norm per
+                                  head with weight mix.norm [vdim], times silu(g h), mix.o                                    */
+/* weights of L3_MIX_WINDOW (L3LayerSpec::attn_kind) */
+#define L3_ATTN_SINK 0
+#define L3_ATTN_SIGMOID 1
 /* feed-forward kinds (L3LayerSpec::ff_kind) */
 #define L3_FF_GLU 0            /* down(act(gate x) * (up x)), act = L3StackConfig::glu_act; experts: down relu(up x)^2 */
 #define L3_FF_POLYNORM 1       /* down(P(up x)),  P(z) = a N(z) + b N(z^2) + c N(z^3) + e with element-wise powers and
@@ -202,6 +221,18 @@ typedef struct L3LayerSpec {
   int32_t ff_kind;           /* L3_FF_* of the dense feed-forward */
   int32_t router_kind;       /* L3_ROUTE_* of the mixture of experts */
   int32_t shared_ff;         /* L3_ROUTE_SIGMOID_IN: width of the shared expert; 0 = none */
+  /* L3_MIX_WINDOW (also uses heads, kv_heads, dim, vdim, scale, window, rot_dims, rot_base) */
+  int32_t keep_first;        /* the first keep_first tokens stay visible behind the window */
+  int32_t attn_kind;         /* L3_ATTN_* */
+  int32_t rot_layout;        /* 0: entry 2i turns with 2i + 1; 1: entry i with i + rot_dims / 2 */
+  int32_t qk_unit;           /* 1: q and k over their root mean square per head, after the rotation */
+  int32_t out_norm_groups;   /* L3_MIX_SSD: parts of the output norm */
+  float tau;                 /* L3_MIX_GLA: the decay is sigmoid(.)^(1 / tau) */
+  /* Two mixers side by side (pre-norm stacks): `pair` (may be null) names a second mixer that reads the same input; the
+   * layer's mixer result is mix_scale * mixer + pair_scale * pair mixer.  The first mixer's tensors are then named
+   * l<i>.mix.left.*, the second's l<i>.mix.right.*; of the pair spec only the mixer fields are read (no ff, no pair). */
+  const struct L3LayerSpec* pair;
+  float mix_scale, pair_scale;
 } L3LayerSpec;
 
 typedef struct L3StackConfig {
@@ -232,6 +263,14 @@ typedef struct L3StackConfig {
    * depth_avg 1: what goes on to the next layer (and to the final norm) is sum_(j <= i+1) dwa_i[j] X_j with X_0 the
    *   embedding output and X_(i+1) layer i's own result (tensor l<i>.dwa [i + 2]). */
   int32_t parallel, norm_center, layer_scale, canon_taps, depth_avg;
+  /* pre-norm stacks: norm_groups G > 1: every layer norm, the embedding norm and the final norm cut the vector into G equal
+   * consecutive parts and divide each by its own root mean square;
+   * embed_norm 1: the embedding rows pass such a norm (tensor embed.norm) before the first layer;
+   * loop_in 1: ahead of every pass of the looped block the stream becomes W [x ; x0] (tensor loop.in [width, 2 width],
+   *   x0 = the embedding output) instead of x + loop.step[pass];
+   * logit_softcap c > 0: logits <- c tanh(logits / c). */
+  int32_t norm_groups, embed_norm, loop_in;
+  float logit_softcap;
 } L3StackConfig;
 
 int l3_create_stack(const L3StackConfig* cfg, const L3LayerSpec* layers, L3Model** out);

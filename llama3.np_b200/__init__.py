@@ -25,6 +25,9 @@ def __getattr__(name):  # lazy: importing the package must not require the built
     if name == "Mabedra":
         from .mabedra import Mabedra
         return Mabedra
+    if name == "Debuzen":
+        from .debuzen import Debuzen
+        return Debuzen
     if name in ("StackDecoder", "StackConfig", "LayerSpec"):
         from . import stack as _s
         return getattr(_s, name)

@@ -25,13 +25,18 @@ class L3Config(C.Structure):
 
 
 MIX_SOFTMAX, MIX_DECAY_LINEAR, MIX_GATED_DELTA, MIX_LATENT, MIX_MINGRU, MIX_DIFF = 0, 1, 2, 3, 4, 5
+MIX_WINDOW, MIX_SSD, MIX_GLA = 6, 7, 8
+ATTN_SINK, ATTN_SIGMOID = 0, 1
 FF_GLU, FF_POLYNORM = 0, 1
 ROUTE_SOFTMAX, ROUTE_SIGMOID_IN = 0, 1
 GLU_SILU, GLU_GELU_TANH = 0, 1
 
 
 class L3LayerSpec(C.Structure):
-    _fields_ = [("mixer", C.c_int32), ("heads", C.c_int32), ("kv_heads", C.c_int32), ("dim", C.c_int32),
+    pass
+
+
+L3LayerSpec._fields_ = [("mixer", C.c_int32), ("heads", C.c_int32), ("kv_heads", C.c_int32), ("dim", C.c_int32),
                 ("vdim", C.c_int32), ("conv_taps", C.c_int32), ("rank_decay", C.c_int32), ("rank_gate", C.c_int32),
                 ("ff", C.c_int32), ("scale", C.c_float), ("decay", C.POINTER(C.c_float)),
                 ("q_rank", C.c_int32), ("kv_rank", C.c_int32), ("rot_dim", C.c_int32), ("rot_dims", C.c_int32),
@@ -40,7 +45,10 @@ class L3LayerSpec(C.Structure):
                 ("groups_keep", C.c_int32), ("router_scale", C.c_float),
                 ("window", C.c_int32), ("diff", C.c_float), ("rot_scale_factor", C.c_float), ("rot_scale_low", C.c_float),
                 ("rot_scale_high", C.c_float), ("rot_scale_original", C.c_int32), ("ff_kind", C.c_int32),
-                ("router_kind", C.c_int32), ("shared_ff", C.c_int32)]
+                ("router_kind", C.c_int32), ("shared_ff", C.c_int32),
+                ("keep_first", C.c_int32), ("attn_kind", C.c_int32), ("rot_layout", C.c_int32), ("qk_unit", C.c_int32),
+                ("out_norm_groups", C.c_int32), ("tau", C.c_float), ("pair", C.POINTER(L3LayerSpec)),
+                ("mix_scale", C.c_float), ("pair_scale", C.c_float)]
 
 
 class L3StackConfig(C.Structure):
@@ -51,7 +59,8 @@ class L3StackConfig(C.Structure):
                 ("norm_input", C.c_int32), ("norm_scalar", C.c_int32), ("token_shift", C.c_int32),
                 ("embed_scale", C.c_float), ("loop_start", C.c_int32), ("loop_stop", C.c_int32), ("loop_times", C.c_int32),
                 ("parallel", C.c_int32), ("norm_center", C.c_int32), ("layer_scale", C.c_int32), ("canon_taps", C.c_int32),
-                ("depth_avg", C.c_int32)]
+                ("depth_avg", C.c_int32), ("norm_groups", C.c_int32), ("embed_norm", C.c_int32), ("loop_in", C.c_int32),
+                ("logit_softcap", C.c_float)]
 
 
 _P = C.c_void_p

@@ -56,14 +56,50 @@ static size_t wb(const L3Model* m) { return m->bf16 ? 2 : 4; }
 static int pad8(int v) { return (v + 7) & ~7; }
 
 // ------------------------------------------------------------------------------ create
+// the mixers that pre-norm stacks run through ll_mix_unit, alone or two side by side
+static bool unit_mixer(int mixer) { return mixer == L3_MIX_WINDOW || mixer == L3_MIX_SSD || mixer == L3_MIX_GLA || mixer == L3_MIX_GATED_DELTA; }
+
+static int check_unit(const L3LayerSpec& s, int i) {
+  REQUIRE(nullptr, s.heads >= 1 && s.dim >= 1 && s.vdim >= 1, "layer %d: bad sizes", i);
+  if (s.mixer == L3_MIX_WINDOW) {
+    REQUIRE(nullptr, s.kv_heads >= 1 && s.heads % s.kv_heads == 0, "layer %d: heads %% kv_heads != 0", i);
+    REQUIRE(nullptr, s.rot_dims >= 0 && s.rot_dims <= s.dim && s.rot_dims % 2 == 0 && (s.rot_dims == 0 || s.rot_base > 0), "layer %d: bad rotary sizes", i);
+    REQUIRE(nullptr, s.window >= 0 && s.keep_first >= 0 && (s.attn_kind == L3_ATTN_SINK || s.attn_kind == L3_ATTN_SIGMOID), "layer %d: bad window / kind", i);
+    REQUIRE(nullptr, win_attn_supported(s.dim, s.vdim), "layer %d: head sizes %d, %d unsupported", i, s.dim, s.vdim);
+  } else if (s.mixer == L3_MIX_SSD) {
+    REQUIRE(nullptr, s.kv_heads >= 1 && s.heads % s.kv_heads == 0, "layer %d: heads %% groups != 0", i);
+    REQUIRE(nullptr, s.conv_taps >= 1 && s.conv_taps <= 64, "layer %d: bad conv size", i);
+    REQUIRE(nullptr, s.out_norm_groups >= 1 && (s.heads * s.vdim) % s.out_norm_groups == 0, "layer %d: bad output norm groups", i);
+    REQUIRE(nullptr, recur_supported(s.dim, s.vdim), "layer %d: state %d x %d unsupported", i, s.dim, s.vdim);
+  } else if (s.mixer == L3_MIX_GLA) {
+    REQUIRE(nullptr, s.rank_decay >= 1 && s.tau > 0.f, "layer %d: bad decay rank / tau", i);
+    REQUIRE(nullptr, recur_supported(s.dim, s.vdim), "layer %d: state %d x %d unsupported", i, s.dim, s.vdim);
+  } else {
+    REQUIRE(nullptr, s.kv_heads >= 1 && s.heads % s.kv_heads == 0, "layer %d: heads %% kv_heads != 0", i);
+    REQUIRE(nullptr, s.conv_taps >= 1 && s.conv_taps <= 64 && s.rank_decay >= 1 && s.rank_gate >= 1, "layer %d: bad conv / rank sizes", i);
+    REQUIRE(nullptr, recur_supported(s.dim, s.vdim), "layer %d: state %d x %d unsupported", i, s.dim, s.vdim);
+  }
+  return L3_OK;
+}
+
 static int check_spec(const L3StackConfig* c, const L3LayerSpec& s, int i) {
-  REQUIRE(nullptr, s.mixer >= L3_MIX_SOFTMAX && s.mixer <= L3_MIX_DIFF, "layer %d: unknown mixer %d", i, s.mixer);
+  REQUIRE(nullptr, s.mixer >= L3_MIX_SOFTMAX && s.mixer <= L3_MIX_GLA, "layer %d: unknown mixer %d", i, s.mixer);
+  REQUIRE(nullptr, s.mixer < L3_MIX_WINDOW || (c->norm_input && !c->parallel), "layer %d: this mixer is built for pre-norm layers (norm_input)", i);
+  REQUIRE(nullptr, !s.pair || (c->norm_input && !c->parallel && unit_mixer(s.mixer) && unit_mixer(s.pair->mixer) && !s.pair->pair),
+          "layer %d: two mixers side by side need a pre-norm stack and mixers of the window / state-space / gated-linear / gated-delta kinds", i);
+  if (c->norm_input && !c->parallel && unit_mixer(s.mixer)) {
+    int rc = check_unit(s, i);
+    if (rc == L3_OK && s.pair) rc = check_unit(*s.pair, i);
+    if (rc != L3_OK) return rc;
+  }
   REQUIRE(nullptr, (s.mixer == L3_MIX_DIFF) == (c->parallel != 0), "layer %d: differential attention and parallel layers come together", i);
   REQUIRE(nullptr, s.ff_kind == L3_FF_GLU || (s.ff_kind == L3_FF_POLYNORM && c->parallel), "layer %d: this feed-forward kind is built for parallel layers", i);
   REQUIRE(nullptr, s.router_kind == L3_ROUTE_SOFTMAX || (s.router_kind == L3_ROUTE_SIGMOID_IN && c->parallel), "layer %d: this router kind is built for parallel layers", i);
   REQUIRE(nullptr, !(c->parallel && s.experts > 0) || s.router_kind == L3_ROUTE_SIGMOID_IN, "layer %d: parallel layers take the sigmoid router", i);
   REQUIRE(nullptr, s.heads >= 1 && s.dim >= 1 && s.vdim >= 1 && s.ff >= 0, "layer %d: bad sizes", i);
   REQUIRE(nullptr, s.mixer <= L3_MIX_GATED_DELTA || c->norm_input, "layer %d: this mixer is built for pre-norm layers (norm_input)", i);
+  REQUIRE(nullptr, !(c->norm_input && !c->parallel) || s.mixer == L3_MIX_LATENT || s.mixer == L3_MIX_MINGRU || unit_mixer(s.mixer),
+          "layer %d: mixer %d is not built for pre-norm layers", i, s.mixer);
   if (s.experts > 0) {
     const int n = s.experts + s.identity;
     REQUIRE(nullptr, c->norm_input, "layer %d: the mixture of experts is built for pre-norm layers (norm_input)", i);
@@ -90,12 +126,59 @@ static int check_spec(const L3StackConfig* c, const L3LayerSpec& s, int i) {
   } else if (s.mixer == L3_MIX_DECAY_LINEAR) {
     REQUIRE(nullptr, s.decay != nullptr, "layer %d: decay-linear mixer without decays", i);
     REQUIRE(nullptr, recur_supported(s.dim, s.vdim), "layer %d: state %d x %d unsupported", i, s.dim, s.vdim);
-  } else {
+  } else if (s.mixer == L3_MIX_GATED_DELTA) {
     REQUIRE(nullptr, s.kv_heads >= 1 && s.heads % s.kv_heads == 0, "layer %d: heads %% kv_heads != 0", i);
     REQUIRE(nullptr, s.conv_taps >= 1 && s.conv_taps <= 64 && s.rank_decay >= 1 && s.rank_gate >= 1, "layer %d: bad conv / rank sizes", i);
     REQUIRE(nullptr, recur_supported(s.dim, s.vdim), "layer %d: state %d x %d unsupported", i, s.dim, s.vdim);
   }
   (void)c;
+  return L3_OK;
+}
+
+// Segment layout of a unit mixer's share of the fused input projection (offsets relative to the unit's first column),
+// the width of its share of the output projection's input, and its small fp32 tensors.
+static int ll_alloc_unit(LLLayer& L, size_t w) {
+  const L3LayerSpec& s = L.spec;
+  const int H = s.heads, G = s.kv_heads, DK = s.dim, DV = s.vdim;
+  cudaError_t e = cudaSuccess;
+  auto al = [&](void** p, size_t bytes) { if (e == cudaSuccess) e = cudaMalloc(p, std::max<size_t>(16, bytes)); };
+  L.n_ctx = H * DV;
+  if (s.mixer == L3_MIX_WINDOW) {
+    L.off_q = 0; L.off_k = H * DK; L.off_v = L.off_k + G * DK; L.n_in = pad8(L.off_v + G * DV);  // q | k | v
+    al((void**)&L.head_vec, (size_t)H * 4);
+    al((void**)&L.inv_freq, (size_t)std::max(1, s.rot_dims / 2) * 4);
+    std::vector<float> f(std::max(1, s.rot_dims / 2), 0.f);
+    for (int j = 0; j < s.rot_dims / 2; ++j) f[j] = (float)pow(s.rot_base, -2.0 * j / s.rot_dims);
+    if (e == cudaSuccess) e = cudaMemcpy(L.inv_freq, f.data(), f.size() * 4, cudaMemcpyHostToDevice);
+  } else if (s.mixer == L3_MIX_SSD) {
+    // z | x | B | C | dt as the checkpoint lays them out: x, B, C stay contiguous (a convolution channel is a column)
+    const int inner = H * DV, gn = G * DK;
+    L.off_g = 0; L.off_q = inner; L.off_b = 2 * inner + 2 * gn; L.n_in = pad8(L.off_b + H);
+    al((void**)&L.conv_w, (size_t)(inner + 2 * gn) * s.conv_taps * 4);
+    al((void**)&L.conv_b, (size_t)(inner + 2 * gn) * 4);
+    al((void**)&L.A_log, (size_t)H * 4);
+    al((void**)&L.dt_bias, (size_t)H * 4);
+    al((void**)&L.skip_d, (size_t)H * 4);
+    al((void**)&L.mix_norm, (size_t)inner * 4);
+  } else if (s.mixer == L3_MIX_GLA) {
+    L.off_q = 0; L.off_k = H * DK; L.off_v = 2 * H * DK; L.off_g = L.off_v + H * DV;
+    L.off_a1 = pad8(L.off_g + H * DV); L.n_in = pad8(L.off_a1 + s.rank_decay);
+    al((void**)&L.mix_norm, (size_t)DV * 4);
+    al(&L.w_a2, (size_t)H * DK * s.rank_decay * w);
+    al((void**)&L.a2_bias, (size_t)H * DK * 4);
+  } else {
+    // q | k | v stay contiguous (a convolution channel is a column); the inner projections start on a
+    // multiple of 8 columns so that the second-stage projections read 16-byte aligned rows
+    L.off_q = 0; L.off_k = G * DK; L.off_v = 2 * G * DK; L.off_b = L.off_v + H * DV;
+    L.off_a1 = pad8(L.off_b + H); L.off_g1 = pad8(L.off_a1 + s.rank_decay); L.n_in = pad8(L.off_g1 + s.rank_gate);
+    al((void**)&L.mix_norm, (size_t)DV * 4);
+    al(&L.w_a2, (size_t)H * DK * s.rank_decay * w);
+    al(&L.w_g2, (size_t)H * DV * s.rank_gate * w);
+    al((void**)&L.conv_w, (size_t)(2 * G * DK + H * DV) * s.conv_taps * 4);
+    al((void**)&L.A_log, (size_t)H * 4);
+    al((void**)&L.dt_bias, (size_t)H * DK * 4);
+  }
+  if (e != cudaSuccess) { set_err(nullptr, "cudaMalloc of a mixer's tensors failed: %s", cudaGetErrorString(e)); return L3_ENOMEM; }
   return L3_OK;
 }
 
@@ -116,6 +199,11 @@ extern "C" int l3_create_stack(const L3StackConfig* c, const L3LayerSpec* specs,
   REQUIRE(nullptr, !c->parallel || (c->norm_input && !c->token_shift && !c->norm_scalar && c->loop_times == 0), "parallel layers are pre-norm layers without token shift, single-weight norms or loops");
   REQUIRE(nullptr, c->parallel || (!c->norm_center && !c->layer_scale && !c->canon_taps && !c->depth_avg), "centred norms, layer scales, input convolutions and the depth average are built for parallel layers");
   REQUIRE(nullptr, c->canon_taps >= 0 && c->canon_taps <= 64, "bad canon_taps");
+  REQUIRE(nullptr, c->norm_groups >= 0 && c->norm_groups <= 32 && (c->norm_groups <= 1 || c->width % c->norm_groups == 0), "bad norm_groups");
+  REQUIRE(nullptr, (c->norm_input && !c->parallel) || (c->norm_groups <= 1 && !c->embed_norm && !c->loop_in && !(c->logit_softcap > 0.f)),
+          "grouped norms, the embedding norm, the loop's entry projection and the logit cap are built for pre-norm stacks");
+  REQUIRE(nullptr, !c->loop_in || c->loop_times > 0, "loop_in without a loop");
+  REQUIRE(nullptr, !(c->norm_groups > 1 && c->norm_scalar), "grouped norms have one weight per coordinate");
   L3Model* m = new L3Model();
   LayerList* ll = m->ll = new LayerList();
   ll->cfg = *c;
@@ -154,7 +242,19 @@ extern "C" int l3_create_stack(const L3StackConfig* c, const L3LayerSpec* specs,
     const L3LayerSpec& s = L.spec;
     const int H = s.heads, G = s.mixer == L3_MIX_DECAY_LINEAR ? s.heads : s.kv_heads, DK = s.dim, DV = s.vdim;
     L.spec.kv_heads = G;
-    if (s.mixer == L3_MIX_LATENT) {
+    if (s.pair) {  // the second mixer of the layer: its own record, sharing the first one's projections
+      L.pair = new LLLayer();
+      L.pair->spec = *s.pair;
+      L.pair->spec.pair = nullptr; L.pair->spec.ff = 0; L.pair->spec.experts = 0; L.pair->spec.decay = nullptr;
+      L.pair->mix_scale = s.pair_scale;
+      L.mix_scale = s.mix_scale;
+      L.spec.pair = nullptr;  // the caller's record is not kept
+    }
+    if (unit_mixer(s.mixer) && c->norm_input) {
+      int rc = ll_alloc_unit(L, w);
+      if (rc == L3_OK && L.pair) rc = ll_alloc_unit(*L.pair, w);
+      if (rc != L3_OK) { l3_destroy(m); return rc; }
+    } else if (s.mixer == L3_MIX_LATENT) {
       // dq | dkv | g rows, every segment on a multiple of 8 columns of the projection's output
       const int Dk = s.kv_rank + s.rot_dim;
       L.off_q = 0; L.off_k = pad8(s.q_rank); L.off_g = pad8(L.off_k + Dk); L.n_in = pad8(L.off_g + H);
@@ -222,10 +322,15 @@ extern "C" int l3_create_stack(const L3StackConfig* c, const L3LayerSpec* specs,
       AL(L.A_log, (size_t)H * 4);
       AL(L.dt_bias, (size_t)H * DK * 4);
     }
+    const int n_ctx = (s.mixer == L3_MIX_MINGRU ? DK : H * DV) + (L.pair ? L.pair->n_ctx : 0);  // columns the output projection reads
+    L.n_ctx = n_ctx - (L.pair ? L.pair->n_ctx : 0);
+    L.in_base = 0; L.ctx_base = 0; L.ctx_ld = n_ctx;
+    if (L.pair) { L.pair->in_base = L.n_in; L.pair->ctx_base = L.n_ctx; L.pair->ctx_ld = n_ctx; L.n_in += L.pair->n_in; L.pair->in_ld = L.n_in; }
+    L.in_ld = L.n_in;  // n_in: the rows of the whole fused projection
     AL(L.w_in, (size_t)L.n_in * W * w);
     cudaMemset(L.w_in, 0, (size_t)L.n_in * W * w);  // padding rows project to zero
-    const int n_ctx = s.mixer == L3_MIX_MINGRU ? DK : H * DV;  // columns the output projection reads
     AL(L.w_o, (size_t)W * n_ctx * w);
+    if (L.pair) { L.pair->w_in = (char*)L.w_in + (size_t)L.pair->in_base * W * w; L.pair->w_o = (char*)L.w_o + (size_t)L.pair->ctx_base * w; }
     AL(L.norm1, (size_t)W * 4);
     if (c->token_shift) AL(L.shift, (size_t)W * 4);
     if (c->layer_scale) { AL(L.ls1, (size_t)W * 4); if (s.ff > 0) AL(L.ls2, (size_t)W * 4); }
@@ -257,12 +362,15 @@ extern "C" int l3_create_stack(const L3StackConfig* c, const L3LayerSpec* specs,
       AL(L.side_norm, (size_t)W * 4);
     }
     ll->max_in = std::max(ll->max_in, L.n_in);
-    ll->max_o = std::max(ll->max_o, std::max(H * DV, H * DK));
+    ll->max_o = std::max(ll->max_o, std::max(std::max(H * DV, H * DK), n_ctx));
+    if (L.pair) ll->max_o = std::max(ll->max_o, std::max(L.pair->spec.heads * L.pair->spec.vdim, L.pair->spec.heads * L.pair->spec.dim));
     if (L.ff_total) ll->max_ff = std::max(ll->max_ff, L.ff_total);
     if (s.mixer == L3_MIX_LATENT) ll->max_o = std::max(ll->max_o, H * s.kv_rank);
     ll->max_ff = std::max(ll->max_ff, s.experts > 0 ? s.experts * s.ff : s.ff);
   }
-  if (c->loop_times > 0) AL(ll->loop_step, (size_t)c->loop_times * W * 4);
+  if (c->loop_times > 0 && !c->loop_in) AL(ll->loop_step, (size_t)c->loop_times * W * 4);
+  if (c->loop_in) AL(ll->loop_in, (size_t)W * 2 * W * w);
+  if (c->embed_norm) AL(ll->embed_norm, (size_t)W * 4);
 #undef AL
   // execution order: the layers ahead of the loop, the looped block loop_times times, the rest
   auto run = [&](int layer, int pass) { LLRun r; r.layer = layer; r.pass = pass; ll->runs.push_back(r); };
@@ -291,6 +399,86 @@ struct LLPlace {
   bool broadcast = false;  // the checkpoint holds one number, the device vector `rows` copies of it
   float scale = 0.f, bias = 0.f;  // random init
 };
+
+// Tensors of a unit mixer (window attention, state-space, gated linear attention, gated delta rule); r = "mix.<name>"
+static bool ll_place_unit(L3Model* m, LLLayer& L, const std::string& r, LLPlace* p) {
+  const int W = m->ll->cfg.width;
+  const L3LayerSpec& s = L.spec;
+  const int H = s.heads, G = s.kv_heads, DK = s.dim, DV = s.vdim;
+  auto mat = [&](void* d, int64_t rows, int64_t cols, int row0 = 0) {
+    p->dst = d; p->wt = true; p->rows = rows; p->cols = cols; p->row0 = row0; p->row_stride = 1; p->ld = (int)cols;
+    p->scale = 1.0f / sqrtf((float)cols);
+    return d != nullptr;
+  };
+  auto vec = [&](float* d, int64_t n, float bias, float scale) {
+    p->dst = d; p->wt = false; p->rows = n; p->cols = 1; p->ld = 1; p->bias = bias; p->scale = scale;
+    return d != nullptr;
+  };
+  auto seg = [&](int off, int64_t rows, float mul = 1.f) { const bool ok = mat(L.w_in, rows, W, off); p->scale *= mul; return ok; };
+  auto conv = [&](int ch0, int64_t rows) {
+    p->dst = L.conv_w + (size_t)ch0 * s.conv_taps; p->wt = false; p->rows = rows; p->cols = s.conv_taps; p->ld = s.conv_taps;
+    p->scale = 1.0f / sqrtf((float)s.conv_taps);
+    return true;
+  };
+  if (r == "mix.o") {  // this mixer's columns of the layer's output projection
+    const bool ok = mat(L.w_o, W, L.n_ctx);
+    p->ld = L.ctx_ld;
+    return ok;
+  }
+  if (s.mixer == L3_MIX_WINDOW) {
+    if (r == "mix.q") return seg(L.off_q, (int64_t)H * DK, 2.f);
+    if (r == "mix.k") return seg(L.off_k, (int64_t)G * DK, 2.f);
+    if (r == "mix.v") return seg(L.off_v, (int64_t)G * DV);
+    if (r == "mix.sink") return s.attn_kind == L3_ATTN_SINK && vec(L.head_vec, H, 0.5f, 0.5f);
+    if (r == "mix.pb") return s.attn_kind == L3_ATTN_SIGMOID && vec(L.head_vec, H, -2.f, 0.5f);
+    return false;
+  }
+  if (s.mixer == L3_MIX_SSD) {
+    const int inner = H * DV, gn = G * DK;
+    if (r == "mix.in") return seg(0, (int64_t)2 * inner + 2 * gn + H);
+    if (r == "mix.conv") return conv(0, inner + 2 * gn);
+    if (r == "mix.conv.b") return vec(L.conv_b, inner + 2 * gn, 0.f, 0.1f);
+    if (r == "mix.dt_bias") return vec(L.dt_bias, H, -1.f, 0.5f);
+    if (r == "mix.A_log") return vec(L.A_log, H, 0.f, 0.5f);
+    if (r == "mix.D") return vec(L.skip_d, H, 1.f, 0.2f);
+    if (r == "mix.norm") return vec(L.mix_norm, inner, 1.f, 0.1f);
+    return false;
+  }
+  if (s.mixer == L3_MIX_GLA) {
+    if (r == "mix.q") return seg(L.off_q, (int64_t)H * DK, 2.f);
+    if (r == "mix.k") return seg(L.off_k, (int64_t)H * DK, 2.f);
+    if (r == "mix.v") return seg(L.off_v, (int64_t)H * DV);
+    if (r == "mix.g") return seg(L.off_g, (int64_t)H * DV);
+    if (r == "mix.a1") return seg(L.off_a1, s.rank_decay);
+    if (r == "mix.a2") return mat(L.w_a2, (int64_t)H * DK, s.rank_decay);
+    if (r == "mix.a2.b") return vec(L.a2_bias, (int64_t)H * DK, 3.f, 1.f);
+    if (r == "mix.norm") return vec(L.mix_norm, DV, 1.f, 0.1f);
+    return false;
+  }
+  const int nq = G * DK, nv = H * DV;
+  if (r == "mix.q") return seg(L.off_q, nq, 2.f);
+  if (r == "mix.k") return seg(L.off_k, nq, 2.f);
+  if (r == "mix.v") return seg(L.off_v, nv, 2.f);
+  if (r == "mix.b") return seg(L.off_b, H);
+  if (r == "mix.a1") return seg(L.off_a1, s.rank_decay);
+  if (r == "mix.g1") return seg(L.off_g1, s.rank_gate);
+  if (r == "mix.a2") return mat(L.w_a2, (int64_t)H * DK, s.rank_decay);
+  if (r == "mix.g2") return mat(L.w_g2, nv, s.rank_gate);
+  if (r == "mix.norm") return vec(L.mix_norm, DV, 1.f, 0.1f);
+  if (r == "mix.A_log") return vec(L.A_log, H, 0.f, 0.5f);
+  if (r == "mix.dt_bias") return vec(L.dt_bias, (int64_t)H * DK, -1.f, 0.5f);
+  if (r == "mix.q.conv") return conv(0, nq);
+  if (r == "mix.k.conv") return conv(nq, nq);
+  if (r == "mix.v.conv") return conv(2 * nq, nv);
+  return false;
+}
+
+static std::vector<const char*> ll_unit_names(const L3LayerSpec& s) {
+  if (s.mixer == L3_MIX_WINDOW) return {"q", "k", "v", s.attn_kind == L3_ATTN_SIGMOID ? "pb" : "sink", "o"};
+  if (s.mixer == L3_MIX_SSD) return {"in", "conv", "conv.b", "dt_bias", "A_log", "D", "norm", "o"};
+  if (s.mixer == L3_MIX_GLA) return {"q", "k", "v", "g", "a1", "a2", "a2.b", "norm", "o"};
+  return {"q", "k", "v", "b", "a1", "a2", "g1", "g2", "norm", "A_log", "dt_bias", "q.conv", "k.conv", "v.conv", "o"};
+}
 
 static bool ll_place(L3Model* m, const std::string& name, LLPlace* p) {
   LayerList* ll = m->ll;
@@ -322,6 +510,8 @@ static bool ll_place(L3Model* m, const std::string& name, LLPlace* p) {
   if (name == "head") return mat(m->lm_head, V, W);
   if (name == "final.norm") return norm(m->norm_final);
   if (name == "loop.step") return ll->loop_step && fmat(ll->loop_step, ll->cfg.loop_times, W, 0.3f);
+  if (name == "loop.in") { const bool ok = ll->loop_in && mat(ll->loop_in, W, (int64_t)2 * W); p->scale *= 1.4f; return ok; }
+  if (name == "embed.norm") return ll->embed_norm && norm(ll->embed_norm);
   if (name == "side.embed") { const bool ok = sd && mat(ll->side_embed, V, (int64_t)NL * sd); p->scale = 1.0f; return ok; }
   int li = -1, n = 0;
   if (sscanf(name.c_str(), "l%d.%n", &li, &n) < 1 || n == 0 || li < 0 || li >= NL) return false;
@@ -384,6 +574,12 @@ static bool ll_place(L3Model* m, const std::string& name, LLPlace* p) {
   if (r == "side.gate") return sd && mat(L.side_gate, sd, W);
   if (r == "side.proj") return sd && mat(L.side_proj, W, sd);
   if (r == "side.norm") return sd && vec(L.side_norm, W, 1.f, 0.1f);
+  if (pre && !ll->cfg.parallel && unit_mixer(s.mixer)) {
+    if (!L.pair) return ll_place_unit(m, L, r, p);
+    if (r.compare(0, 9, "mix.left.") == 0) return ll_place_unit(m, L, "mix." + r.substr(9), p);
+    if (r.compare(0, 10, "mix.right.") == 0) return ll_place_unit(m, *L.pair, "mix." + r.substr(10), p);
+    return false;
+  }
   if (r == "mix.o") return mat(L.w_o, W, s.mixer == L3_MIX_MINGRU ? (int64_t)DK : (int64_t)H * DV);
   auto seg = [&](int off, int64_t rows) { const bool ok = mat(L.w_in, rows, W, off, 1); return ok; };
   if (s.mixer == L3_MIX_LATENT) {
@@ -465,12 +661,20 @@ static std::vector<std::string> ll_expected(const L3Model* m) {
   std::vector<std::string> v = {"embed", "head", "final.norm"};
   if (ll->cfg.side_dim) v.push_back("side.embed");
   if (ll->loop_step) v.push_back("loop.step");
+  if (ll->loop_in) v.push_back("loop.in");
+  if (ll->embed_norm) v.push_back("embed.norm");
   for (int i = 0; i < ll->cfg.n_layers; ++i) {
     const L3LayerSpec& s = ll->layers[i].spec;
     const std::string p = "l" + std::to_string(i) + ".";
-    std::vector<const char*> names = {"norm1", "mix.o"};
+    const bool unit = ll->cfg.norm_input && !ll->cfg.parallel && unit_mixer(s.mixer);
+    std::vector<const char*> names = {"norm1"};
+    if (!unit) names.push_back("mix.o");
     if (ll->cfg.token_shift) names.push_back("shift");
-    if (s.mixer == L3_MIX_LATENT) names.insert(names.end(), {"mix.dq", "mix.dq.norm", "mix.uq", "mix.dkv", "mix.dkv.norm", "mix.uk", "mix.uv", "mix.g"});
+    if (unit) {
+      const LLLayer& Lu = ll->layers[i];
+      for (auto nme : ll_unit_names(s)) v.push_back(p + (Lu.pair ? "mix.left." : "mix.") + nme);
+      if (Lu.pair) for (auto nme : ll_unit_names(Lu.pair->spec)) v.push_back(p + "mix.right." + nme);
+    } else if (s.mixer == L3_MIX_LATENT) names.insert(names.end(), {"mix.dq", "mix.dq.norm", "mix.uq", "mix.dkv", "mix.dkv.norm", "mix.uk", "mix.uv", "mix.g"});
     else if (s.mixer == L3_MIX_MINGRU) names.insert(names.end(), {"mix.z", "mix.z.b", "mix.x", "mix.x.b", "mix.g"});
     else if (s.mixer == L3_MIX_DIFF) names.insert(names.end(), {"mix.q", "mix.q.b", "mix.k", "mix.k.b", "mix.v", "mix.v.b", "mix.q.norm", "mix.k.norm",
                                                                 "mix.lq1", "mix.lk1", "mix.lq2", "mix.lk2"});
@@ -561,6 +765,43 @@ int ll_fill_random(L3Model* m, uint64_t seed) {
 }
 
 // ------------------------------------------------------------------------------ finalize / destroy / state
+// channels of a unit mixer's short convolutions (0: it has none)
+static int unit_conv_channels(const L3LayerSpec& s) {
+  if (s.mixer == L3_MIX_SSD) return s.heads * s.vdim + 2 * s.kv_heads * s.dim;
+  if (s.mixer == L3_MIX_GATED_DELTA) return 2 * s.kv_heads * s.dim + s.heads * s.vdim;
+  return 0;
+}
+
+// what a unit mixer keeps per sequence slot: KV caches (window attention) or a state matrix per head (+ convolution tail)
+static int ll_alloc_unit_state(L3Model* m, const L3LayerSpec& s, LLState& St) {
+  const size_t kvb = m->bf16 ? 2 : 4;
+  if (s.mixer == L3_MIX_WINDOW) {
+    CK(m, cudaMalloc(&St.ck, (size_t)m->maxB * s.kv_heads * m->M * s.dim * kvb));
+    CK(m, cudaMalloc(&St.cv, (size_t)m->maxB * s.kv_heads * m->M * s.vdim * kvb));
+    return L3_OK;
+  }
+  CK(m, cudaMalloc((void**)&St.S, (size_t)m->maxB * s.heads * s.dim * s.vdim * 4));
+  const int C = unit_conv_channels(s);
+  if (C) CK(m, cudaMalloc((void**)&St.conv_tail, std::max<size_t>(16, (size_t)m->maxB * C * (s.conv_taps - 1) * 4)));
+  return L3_OK;
+}
+
+static int ll_reset_unit_state(L3Model* m, const L3LayerSpec& s, LLState& St, int slot0, int n, bool kv_too) {
+  const size_t kvb = m->bf16 ? 2 : 4;
+  if (s.mixer == L3_MIX_WINDOW) {
+    if (!kv_too) return L3_OK;  // rows past a slot's position are never read: a new sequence overwrites them
+    const size_t pk = (size_t)s.kv_heads * m->M * s.dim * kvb, pv = (size_t)s.kv_heads * m->M * s.vdim * kvb;
+    CK(m, cudaMemsetAsync((char*)St.ck + slot0 * pk, 0, n * pk, m->stream));
+    CK(m, cudaMemsetAsync((char*)St.cv + slot0 * pv, 0, n * pv, m->stream));
+    return L3_OK;
+  }
+  const size_t per = (size_t)s.heads * s.dim * s.vdim;
+  CK(m, cudaMemsetAsync(St.S + slot0 * per, 0, n * per * 4, m->stream));
+  const size_t pc = (size_t)unit_conv_channels(s) * (s.conv_taps - 1);
+  if (pc) CK(m, cudaMemsetAsync(St.conv_tail + slot0 * pc, 0, n * pc * 4, m->stream));
+  return L3_OK;
+}
+
 int ll_finalize(L3Model* m) {
   LayerList* ll = m->ll;
   for (const auto& name : ll_expected(m))
@@ -575,7 +816,11 @@ int ll_finalize(L3Model* m) {
     const int H = s.heads, G = s.kv_heads, DK = s.dim, DV = s.vdim;
     if (ll->cfg.token_shift) CK(m, cudaMalloc((void**)&St.hprev, (size_t)m->maxB * m->D * 4));
     if (ll->cfg.canon_taps > 1) CK(m, cudaMalloc((void**)&St.conv_tail, (size_t)m->maxB * m->D * (ll->cfg.canon_taps - 1) * 4));
-    if (s.mixer == L3_MIX_LATENT) {
+    if (ll->cfg.norm_input && !ll->cfg.parallel && unit_mixer(s.mixer)) {
+      int rc = ll_alloc_unit_state(m, s, St);
+      if (rc == L3_OK && L.pair) { St.pair = new LLState(); rc = ll_alloc_unit_state(m, L.pair->spec, *St.pair); }
+      if (rc != L3_OK) return rc;
+    } else if (s.mixer == L3_MIX_LATENT) {
       CK(m, cudaMalloc(&St.lat, (size_t)m->maxB * m->M * (s.kv_rank + s.rot_dim) * kvb));
     } else if (s.mixer == L3_MIX_DIFF) {
       CK(m, cudaMalloc(&St.ck, (size_t)m->maxB * 2 * G * m->M * DK * kvb));
@@ -592,9 +837,31 @@ int ll_finalize(L3Model* m) {
       }
     }
   }
+  const bool units = ll->cfg.norm_input && !ll->cfg.parallel;
+  int max_xs = 0;
+  size_t win_part = 0;
+  for (auto& L0 : ll->layers)
+    for (const LLLayer* U = &L0; units && U; U = U->pair) {  // the unit mixers' share of the workspace
+      const L3LayerSpec& s = U->spec;
+      const int H = s.heads, G = s.kv_heads, DK = s.dim, DV = s.vdim;
+      if (s.mixer == L3_MIX_WINDOW) {
+        max_rq = std::max(max_rq, H * DK);
+        win_part = std::max(win_part, win_attn_part_floats(m->maxB * 8, H, DV, 32));
+      } else if (s.mixer == L3_MIX_SSD) {
+        max_rq = std::max(max_rq, G * DK); max_rk = std::max(max_rk, G * DK); max_rv = std::max(max_rv, H * DV);
+        max_rg = std::max(max_rg, H); max_xs = std::max(max_xs, H * DV);
+      } else if (s.mixer == L3_MIX_GLA) {
+        max_rq = std::max(max_rq, H * DK); max_rg = std::max(max_rg, H * DK); max_aux = std::max(max_aux, H * DK);
+      }
+    }
   for (auto& L : ll->layers) {
     const L3LayerSpec& s = L.spec;
     const int H = s.heads, G = s.kv_heads, DK = s.dim, DV = s.vdim;
+    if (L.pair && L.pair->spec.mixer == L3_MIX_GATED_DELTA) {
+      const L3LayerSpec& r = L.pair->spec;
+      max_rq = std::max(max_rq, r.kv_heads * r.dim); max_rk = std::max(max_rk, r.kv_heads * r.dim); max_rv = std::max(max_rv, r.heads * r.vdim);
+      max_rg = std::max(max_rg, r.heads * r.dim); max_h = std::max(max_h, r.heads); max_aux = std::max(max_aux, r.heads * r.dim + r.heads * r.vdim);
+    }
     for (int k = 0; k < 2; ++k) {  // the convolutions' taps, tap-major for the kernels
       float* src = k ? L.canon2 : L.canon1;
       float** dst = k ? &L.canon2t : &L.canon1t;
@@ -639,6 +906,15 @@ int ll_finalize(L3Model* m) {
   CK(m, cudaMalloc((void**)&ll->o, ct * ll->max_o * 4));
   CK(m, cudaMalloc((void**)&ll->sg, ct * std::max(1, sd) * 4));
   if (max_qlat) CK(m, cudaMalloc((void**)&ll->qlat, ct * max_qlat * 4));
+  if (max_xs) CK(m, cudaMalloc((void**)&ll->xs, ct * max_xs * 4));
+  if (win_part) {
+    CK(m, cudaMalloc((void**)&ll->win_part_o, win_part * 4));
+    CK(m, cudaMalloc((void**)&ll->win_part_ml, win_part * 4));
+  }
+  if (ll->cfg.loop_in) {
+    CK(m, cudaMalloc((void**)&ll->x0, ct * W * 4));
+    CK(m, cudaMalloc((void**)&ll->cat, ct * 2 * W * 4));
+  }
   if (ll->cfg.parallel) {
     if (ll->cfg.depth_avg) CK(m, cudaMalloc((void**)&ll->Xs, (size_t)(ll->cfg.n_layers + 1) * ct * W * 4));
     if (ll->cfg.canon_taps > 0) {
@@ -682,6 +958,7 @@ int ll_finalize(L3Model* m) {
     CK(m, cudaMalloc(&ll->sg16, ct * std::max(1, sd) * 2));
     if (max_qlat) CK(m, cudaMalloc(&ll->aux16, ct * max_aux * 2));
     if (ll->hf) CK(m, cudaMalloc(&ll->hf16, ct * W * 2));
+    if (ll->cat) CK(m, cudaMalloc(&ll->cat16, ct * 2 * W * 2));
   }
   m->max_split = 32;
   int max_hn = 1, max_hd = 1;
@@ -725,8 +1002,19 @@ void ll_destroy(L3Model* m) {
     fr(L.A_log); fr(L.dt_bias); fr(L.decay);
     fr(L.w_uq); fr(L.w_uk); fr(L.w_uv); fr(L.inv_freq); fr(L.in_bias); fr(L.shift); fr(L.router); fr(L.correction);
     fr(L.canon1); fr(L.canon2); fr(L.canon1t); fr(L.canon2t); fr(L.ls1); fr(L.ls2); fr(L.dwa); fr(L.lam_vec); fr(L.lambda); fr(L.poly);
+    fr(L.head_vec); fr(L.conv_b); fr(L.skip_d); fr(L.a2_bias);
+    if (LLLayer* R = L.pair) {  // its w_in / w_o are views of the first mixer's
+      fr(R->w_a2); fr(R->w_g2); fr(R->mix_norm); fr(R->conv_w); fr(R->A_log); fr(R->dt_bias); fr(R->inv_freq);
+      fr(R->head_vec); fr(R->conv_b); fr(R->skip_d); fr(R->a2_bias);
+      delete R;
+      L.pair = nullptr;
+    }
   }
-  for (auto& St : ll->state) { fr(St.ck); fr(St.cv); fr(St.S); fr(St.conv_tail); fr(St.lat); fr(St.hprev); }
+  for (auto& St : ll->state) {
+    fr(St.ck); fr(St.cv); fr(St.S); fr(St.conv_tail); fr(St.lat); fr(St.hprev);
+    if (LLState* P = St.pair) { fr(P->ck); fr(P->cv); fr(P->S); fr(P->conv_tail); delete P; St.pair = nullptr; }
+  }
+  fr(ll->loop_in); fr(ll->embed_norm); fr(ll->x0); fr(ll->cat); fr(ll->cat16); fr(ll->win_part_o); fr(ll->win_part_ml); fr(ll->xs);
   fr(ll->diff_part_o); fr(ll->diff_part_ml);
   fr(ll->Xs); fr(ll->hn); fr(ll->hf); fr(ll->hf16); fr(ll->y1); fr(ll->y2); fr(ll->moe_gu);
   fr(ll->loop_step); fr(ll->qlat); fr(ll->aux16); fr(ll->moe_sel); fr(ll->moe_w); fr(ll->moe_dense); fr(ll->moe_idw);
@@ -742,6 +1030,12 @@ int ll_reset_slots(L3Model* m, int slot0, int n, bool kv_too) {
     const L3LayerSpec& s = ll->layers[ll->runs[ri].layer].spec;
     LLState& St = ll->state[ri];
     if (St.hprev) CK(m, cudaMemsetAsync(St.hprev + (size_t)slot0 * m->D, 0, (size_t)n * m->D * 4, m->stream));
+    if (ll->cfg.norm_input && !ll->cfg.parallel && unit_mixer(s.mixer)) {
+      int rc = ll_reset_unit_state(m, s, St, slot0, n, kv_too);
+      if (rc == L3_OK && St.pair) rc = ll_reset_unit_state(m, ll->layers[ll->runs[ri].layer].pair->spec, *St.pair, slot0, n, kv_too);
+      if (rc != L3_OK) return rc;
+      continue;
+    }
     if (s.mixer == L3_MIX_DIFF) {
       if (St.conv_tail) {  // zeros ahead of a sequence's first token
         const size_t pc = (size_t)m->D * (ll->cfg.canon_taps - 1);
@@ -802,10 +1096,13 @@ extern "C" int l3_read_state(L3Model* m, int layer, int slot, float* S_out, floa
   if (!m || !m->finalized) return L3_ESTATE;
   REQUIRE(m, m->ll != nullptr, "l3_read_state needs a handle made by l3_create_stack");
   REQUIRE(m, layer >= 0 && layer < (int)m->ll->runs.size() && slot >= 0 && slot < m->maxB, "layer run / slot out of range");
-  const LLLayer& L = m->ll->layers[m->ll->runs[layer].layer];
-  const LLState& St = m->ll->state[layer];
+  const LLLayer* Lp = &m->ll->layers[m->ll->runs[layer].layer];
+  const LLState* Sp = &m->ll->state[layer];
+  if (Lp->pair && Lp->spec.mixer == L3_MIX_WINDOW) { Lp = Lp->pair; Sp = Sp->pair; }  // two mixers side by side: the recurrent one
+  const LLLayer& L = *Lp;
+  const LLState& St = *Sp;
   const L3LayerSpec& s = L.spec;
-  REQUIRE(m, s.mixer != L3_MIX_SOFTMAX && s.mixer != L3_MIX_DIFF, "layer run %d keeps a KV cache, not a recurrent state (l3_read_cache)", layer);
+  REQUIRE(m, s.mixer != L3_MIX_SOFTMAX && s.mixer != L3_MIX_DIFF && s.mixer != L3_MIX_WINDOW, "layer run %d keeps a KV cache, not a recurrent state (l3_read_cache)", layer);
   CK(m, cudaSetDevice(m->cfg.device));
   CK(m, cudaStreamSynchronize(m->stream));
   if (s.mixer == L3_MIX_LATENT) {
@@ -825,8 +1122,8 @@ extern "C" int l3_read_state(L3Model* m, int layer, int slot, float* S_out, floa
   const size_t per = (size_t)s.heads * s.dim * s.vdim;
   if (S_out) CK(m, cudaMemcpy(S_out, St.S + slot * per, per * 4, cudaMemcpyDeviceToHost));
   if (conv_out) {
-    REQUIRE(m, s.mixer == L3_MIX_GATED_DELTA, "layer run %d has no convolution", layer);
-    const size_t pc = (size_t)(2 * s.kv_heads * s.dim + s.heads * s.vdim) * (s.conv_taps - 1);
+    REQUIRE(m, unit_conv_channels(s) > 0, "layer run %d has no convolution", layer);
+    const size_t pc = (size_t)unit_conv_channels(s) * (s.conv_taps - 1);
     if (pc) CK(m, cudaMemcpy(conv_out, St.conv_tail + slot * pc, pc * 4, cudaMemcpyDeviceToHost));
   }
   return L3_OK;
@@ -909,6 +1206,82 @@ static EpiArgs resid_into(float* x, int ld) {
   return e;
 }
 
+// One unit mixer (window attention, state-space, gated linear attention, gated delta rule) of a pre-norm layer: from its
+// columns of the fused input projection (pin, row stride ld) to its columns of the output projection's input (m->ctx, row
+// stride Ly.ctx_ld, already times the mixer's scale).
+static int ll_mix_unit(L3Model* m, LLLayer& Ly, LLState& St, const float* pin, int ld, int B, int L) {
+  LayerList* ll = m->ll;
+  const L3LayerSpec& s = Ly.spec;
+  const int ntok = B * L, H = s.heads, G = s.kv_heads, DK = s.dim, DV = s.vdim, O = H * DV;
+  const float eps = ll->cfg.norm_eps;
+  int* d_pos = m->d_scal + 0;
+  float* ctx = m->ctx + Ly.ctx_base;
+  bf16* ctx16 = m->ctx16 ? (bf16*)m->ctx16 + Ly.ctx_base : nullptr;
+  int rc;
+  if (s.mixer == L3_MIX_WINDOW) {
+    WinPrepArgs pa{};
+    pa.proj = pin; pa.ld = ld; pa.q_off = Ly.off_q; pa.k_off = Ly.off_k; pa.v_off = Ly.off_v; pa.inv_freq = Ly.inv_freq;
+    pa.rot_dims = s.rot_dims; pa.rot_layout = s.rot_layout; pa.unit_norm = s.qk_unit; pa.eps = eps;
+    pa.q_out = m->q; pa.cache_k = St.ck; pa.cache_v = St.cv; pa.pos_ptr = d_pos;
+    pa.L = L; pa.H = H; pa.G = G; pa.DK = DK; pa.DV = DV; pa.M = m->M;
+    LAUNCH(m, launch_win_prep(pa, ntok, m->bf16, m->stream));
+    WinAttnArgs at{};
+    at.q = m->q; at.cache_k = St.ck; at.cache_v = St.cv; at.out = ctx; at.out16 = ctx16; at.ld_out = Ly.ctx_ld; at.out_scale = Ly.mix_scale;
+    at.head_vec = Ly.head_vec; at.pos_ptr = d_pos; at.scale = s.scale; at.kind = s.attn_kind; at.window = s.window; at.keep_first = s.keep_first;
+    at.B = B; at.L = L; at.H = H; at.G = G; at.DK = DK; at.DV = DV; at.M = m->M;
+    at.nsplit = win_attn_splits(B, L, H, G, s.window, s.keep_first, m->M, 32);
+    at.part_o = ll->win_part_o; at.part_ml = ll->win_part_ml;
+    LAUNCH(m, launch_win_attn(at, m->bf16, m->stream));
+    if (at.nsplit > 1) m->launch_acc += 1;
+    return L3_OK;
+  }
+  MixOutArgs mo{};
+  mo.o = ll->o; mo.n = O; mo.DV = DV; mo.eps = eps; mo.out_scale = Ly.mix_scale; mo.out = ctx; mo.out16 = ctx16; mo.ld_out = Ly.ctx_ld;
+  RecurArgs ra{};
+  ra.state = St.S; ra.out = ll->o; ra.B = B; ra.L = L; ra.H = H; ra.DK = DK; ra.DV = DV;
+  if (s.mixer == L3_MIX_SSD) {
+    const int gn = G * DK;
+    SsdPrepArgs pa{};
+    pa.proj = pin; pa.ld = ld; pa.xbc_off = Ly.off_q; pa.dt_off = Ly.off_b; pa.conv_w = Ly.conv_w; pa.conv_b = Ly.conv_b;
+    pa.conv_tail = St.conv_tail; pa.A_log = Ly.A_log; pa.dt_bias = Ly.dt_bias;
+    pa.x_out = ll->xs; pa.v_out = ll->rv; pa.k_out = ll->rk; pa.q_out = m->q; pa.decay_out = ll->rg;
+    pa.L = L; pa.H = H; pa.G = G; pa.N = DK; pa.DV = DV; pa.taps = s.conv_taps;
+    LAUNCH(m, launch_ssd_prep(pa, ntok, m->stream));
+    if (s.conv_taps > 1) LAUNCH(m, launch_conv_tail(St.conv_tail, pin + Ly.off_q, ld, B, L, O + 2 * gn, s.conv_taps - 1, m->stream));
+    ra.mode = 2; ra.q = m->q; ra.k = ll->rk; ra.v = ll->rv; ra.ld_q = ra.ld_k = gn; ra.ld_v = O; ra.g = ll->rg; ra.g_head = 1; ra.rep = H / G;
+    LAUNCH(m, launch_recur(ra, m->stream));
+    mo.skip_d = Ly.skip_d; mo.skip_x = ll->xs; mo.gate = pin + Ly.off_g; mo.ld_gate = ld; mo.gate_act = 1; mo.pre_gate = 1;
+    mo.w = Ly.mix_norm; mo.wlen = O; mo.group = O / s.out_norm_groups;
+  } else if (s.mixer == L3_MIX_GLA) {
+    const int nd = H * DK;
+    float* z = ll->aux;  // [ntok, H * DK] decay logits
+    if ((rc = ll_linear(m, Ly.w_a2, pin + Ly.off_a1, nullptr, ld, ntok, nd, s.rank_decay, EPI_STORE, store_to(z, nullptr, nd))) != L3_OK) return rc;
+    LAUNCH(m, launch_gla_prep(pin + Ly.off_q, ld, 1.0f / sqrtf((float)DK), z, nd, Ly.a2_bias, s.tau, ntok, nd, m->q, ll->rg, m->stream));
+    ra.mode = 2; ra.q = m->q; ra.ld_q = nd; ra.k = pin + Ly.off_k; ra.ld_k = ld; ra.v = pin + Ly.off_v; ra.ld_v = ld; ra.g = ll->rg; ra.rep = 1;
+    LAUNCH(m, launch_recur(ra, m->stream));
+    mo.gate = pin + Ly.off_g; mo.ld_gate = ld; mo.gate_act = 1; mo.pre_gate = 0; mo.w = Ly.mix_norm; mo.wlen = DV; mo.group = DV;
+  } else {
+    const int nq = G * DK, nd = H * DK;
+    float* dt = ll->aux;                          // [ntok, H * DK] decay logits
+    float* og = ll->aux + (size_t)ntok * nd;      // [ntok, H * DV] output-gate logits
+    if ((rc = ll_linear(m, Ly.w_a2, pin + Ly.off_a1, nullptr, ld, ntok, nd, s.rank_decay, EPI_STORE, store_to(dt, nullptr, nd))) != L3_OK) return rc;
+    if ((rc = ll_linear(m, Ly.w_g2, pin + Ly.off_g1, nullptr, ld, ntok, O, s.rank_gate, EPI_STORE, store_to(og, nullptr, O))) != L3_OK) return rc;
+    DeltaPrepArgs pa{};
+    pa.proj = pin; pa.ld = ld; pa.beta_off = Ly.off_b; pa.dt_in = dt; pa.ld_dt = nd;
+    pa.conv_w = Ly.conv_w; pa.conv_tail = St.conv_tail; pa.A_log = Ly.A_log; pa.dt_bias = Ly.dt_bias;
+    pa.q_out = m->q; pa.k_out = ll->rk; pa.v_out = ll->rv; pa.decay_out = ll->rg; pa.beta_out = ll->rbeta;
+    pa.L = L; pa.H = H; pa.G = G; pa.DK = DK; pa.DV = DV; pa.taps = s.conv_taps;
+    LAUNCH(m, launch_delta_prep(pa, ntok, m->stream));
+    if (s.conv_taps > 1) LAUNCH(m, launch_conv_tail(St.conv_tail, pin, ld, B, L, 2 * nq + O, s.conv_taps - 1, m->stream));
+    ra.mode = 1; ra.q = m->q; ra.k = ll->rk; ra.v = ll->rv; ra.ld_q = ra.ld_k = nq; ra.ld_v = O;
+    ra.g = ll->rg; ra.beta = ll->rbeta; ra.rep = H / G;
+    LAUNCH(m, launch_recur(ra, m->stream));
+    mo.gate = og; mo.ld_gate = O; mo.gate_act = 0; mo.pre_gate = 0; mo.w = Ly.mix_norm; mo.wlen = DV; mo.group = DV;
+  }
+  LAUNCH(m, launch_mix_out(mo, ntok, m->stream));
+  return L3_OK;
+}
+
 static int ll_enqueue_prenorm(L3Model* m, int B, int L, float* d_resid) {
   LayerList* ll = m->ll;
   const int ntok = B * L, W = m->D;
@@ -919,18 +1292,28 @@ static int ll_enqueue_prenorm(L3Model* m, int B, int L, float* d_resid) {
   int rc;
   ll->xcur = m->x;
   if (ll->cfg.embed_scale != 0.f && ll->cfg.embed_scale != 1.f) LAUNCH(m, launch_scale_add_rows(m->x, ll->cfg.embed_scale, nullptr, ntok, W, m->stream));
+  const int ng = std::max(1, ll->cfg.norm_groups);
+  if (ll->embed_norm) LAUNCH(m, launch_rmsnorm_rows(m->x, ll->embed_norm, eps, ntok, W, 1, 0, nullptr, m->x, nullptr, m->stream, ng));  // in place, row by row
+  if (ll->x0) CK(m, cudaMemcpyAsync(ll->x0, m->x, (size_t)ntok * W * 4, cudaMemcpyDeviceToDevice, m->stream));  // the embedding output
   for (int ri = 0; ri < (int)ll->runs.size(); ++ri) {
     LLLayer& Ly = ll->layers[ll->runs[ri].layer];
     LLState& St = ll->state[ri];
     const L3LayerSpec& s = Ly.spec;
     const int H = s.heads, DK = s.dim, DV = s.vdim;
-    if (ll->runs[ri].pass >= 0)
+    if (ll->runs[ri].pass >= 0 && ll->loop_in) {  // a pass starts: x <- W_in [x ; x0]
+      LAUNCH(m, launch_concat_rows(m->x, ll->x0, ntok, W, ll->cat, (bf16*)ll->cat16, m->stream));
+      if ((rc = ll_linear(m, ll->loop_in, ll->cat, ll->cat16, 0, ntok, W, 2 * W, EPI_STORE, store_to(m->x, nullptr, W))) != L3_OK) return rc;
+    } else if (ll->runs[ri].pass >= 0)
       LAUNCH(m, launch_scale_add_rows(m->x, 1.0f, ll->loop_step + (size_t)ll->runs[ri].pass * W, ntok, W, m->stream));
-    LAUNCH(m, launch_prenorm_shift(m->x, Ly.norm1, eps, Ly.shift, St.hprev, B, L, W, hn, hn16, m->stream));
+    LAUNCH(m, launch_prenorm_shift(m->x, Ly.norm1, eps, Ly.shift, St.hprev, B, L, W, hn, hn16, m->stream, ng));
     // every projection of the mixer's input in one GEMM
     if ((rc = ll_linear(m, Ly.w_in, hn, hn16, 0, ntok, Ly.n_in, W, EPI_STORE, store_to(ll->pin, nullptr, Ly.n_in))) != L3_OK) return rc;
     int n_ctx = H * DV;
-    if (s.mixer == L3_MIX_LATENT) {
+    if (unit_mixer(s.mixer)) {
+      n_ctx = Ly.ctx_ld;
+      if ((rc = ll_mix_unit(m, Ly, St, ll->pin, Ly.in_ld, B, L)) != L3_OK) return rc;
+      if (Ly.pair && (rc = ll_mix_unit(m, *Ly.pair, *St.pair, ll->pin + Ly.pair->in_base, Ly.in_ld, B, L)) != L3_OK) return rc;
+    } else if (s.mixer == L3_MIX_LATENT) {
       const int Dk = s.kv_rank + s.rot_dim, nq = H * (DK + s.rot_dim);
       LatentPrepArgs pa{};
       pa.proj = ll->pin; pa.ld = Ly.n_in; pa.k_off = Ly.off_k; pa.wq = Ly.q_norm; pa.wk = Ly.k_norm; pa.eps = eps;
@@ -975,7 +1358,7 @@ static int ll_enqueue_prenorm(L3Model* m, int B, int L, float* d_resid) {
     if ((rc = ll_linear(m, Ly.w_o, m->ctx, m->ctx16, 0, ntok, W, n_ctx, EPI_RESID, resid_into(m->x, W))) != L3_OK) return rc;
     if (s.experts > 0) {
       const int E = s.experts, ff = s.ff;
-      LAUNCH(m, launch_prenorm_shift(m->x, Ly.norm2, eps, nullptr, nullptr, B, L, W, hn, hn16, m->stream));
+      LAUNCH(m, launch_prenorm_shift(m->x, Ly.norm2, eps, nullptr, nullptr, B, L, W, hn, hn16, m->stream, ng));
       const bool few = ntok <= 8;  // few rows read only their chosen experts' weights; many share one GEMM over all experts
       MoeRouteArgs ra{};
       ra.h = hn; ra.router = Ly.router; ra.correction = Ly.correction; ra.D = W; ra.E = E; ra.I = s.identity; ra.top = s.top;
@@ -992,7 +1375,7 @@ static int ll_enqueue_prenorm(L3Model* m, int B, int L, float* d_resid) {
         if (s.identity > 0) LAUNCH(m, launch_moe_identity(m->x, hn, ll->moe_idw, ntok, W, m->stream));
       }
     } else if (s.ff > 0) {
-      LAUNCH(m, launch_prenorm_shift(m->x, Ly.norm2, eps, nullptr, nullptr, B, L, W, hn, hn16, m->stream));
+      LAUNCH(m, launch_prenorm_shift(m->x, Ly.norm2, eps, nullptr, nullptr, B, L, W, hn, hn16, m->stream, ng));
       EpiArgs e = store_to(m->h, m->h16, s.ff);
       e.act = ll->cfg.glu_act;
       if ((rc = ll_linear(m, Ly.w13, hn, hn16, 0, ntok, 2 * s.ff, W, EPI_SWIGLU, e)) != L3_OK) return rc;
@@ -1227,6 +1610,10 @@ int ll_enqueue_head(L3Model* m, int B, int L, const int32_t* d_rows, int n_rows)
   if (m->ll->cfg.norm_center)
     LAUNCH(m, launch_layernorm_rows(m->ll->xcur, m->norm_final, m->ll->cfg.norm_eps, 1, rows, m->D, L, L - 1, d_rows, m->xlast, (bf16*)m->xlast16, m->stream));
   else
-    LAUNCH(m, launch_rmsnorm_rows(m->ll->xcur, m->norm_final, m->ll->cfg.norm_eps, rows, m->D, L, L - 1, d_rows, m->xlast, (bf16*)m->xlast16, m->stream));
-  return ll_linear(m, m->lm_head, m->xlast, m->xlast16, 0, rows, m->VS, m->D, EPI_STORE, store_to(m->logits, nullptr, m->VS));
+    LAUNCH(m, launch_rmsnorm_rows(m->ll->xcur, m->norm_final, m->ll->cfg.norm_eps, rows, m->D, L, L - 1, d_rows, m->xlast, (bf16*)m->xlast16, m->stream,
+                                  std::max(1, m->ll->cfg.norm_groups)));
+  const int rc = ll_linear(m, m->lm_head, m->xlast, m->xlast16, 0, rows, m->VS, m->D, EPI_STORE, store_to(m->logits, nullptr, m->VS));
+  if (rc != L3_OK) return rc;
+  if (m->ll->cfg.logit_softcap > 0.f) LAUNCH(m, launch_softcap(m->logits, (int64_t)rows * m->VS, m->ll->cfg.logit_softcap, m->stream));
+  return L3_OK;
 }

@@ -48,6 +48,16 @@ struct LLLayer {
   // sigmoid-routed gated experts: w13 = [2 (experts ff + shared_ff), width] rows interleaved (gate_j, up_j), expert by
   // expert, the shared expert last; w2 = [width, experts ff + shared_ff]
   int ff_total = 0;
+  // window attention: head_vec [heads] the sinks' logits or the sigmoid's biases; state-space mixer: conv_b [channels],
+  // skip_d [heads] (the D of y += D x), dt_bias [heads]; gated linear attention: a2_bias [heads * dim]
+  float *head_vec = nullptr, *conv_b = nullptr, *skip_d = nullptr, *a2_bias = nullptr;
+  // Two mixers side by side: `pair` is the second one (its mixer fields only).  Both read ONE fused input projection -
+  // w_in holds in_ld rows, this mixer's segment starts at row / output column in_base - and feed ONE output projection:
+  // w_o is [width, ctx_ld], this mixer's columns start at ctx_base.  A single mixer has in_base = ctx_base = 0.
+  // The pair's w_in / w_o point into the first mixer's allocations.
+  LLLayer* pair = nullptr;
+  int in_base = 0, in_ld = 0, ctx_base = 0, ctx_ld = 0, n_ctx = 0;
+  float mix_scale = 1.f;  // multiplier of this mixer's result (applied to its slice of the output projection's input)
 };
 
 // What one layer RUN keeps per sequence slot (a layer inside the loop has one of these per pass).
@@ -59,6 +69,9 @@ struct LLState {
   float* hprev = nullptr;             // token shift: [maxB, width] the last token's normed mixer input
   // differential attention: ck [maxB, 2 kv_heads, M, dim] (head g, map m at 2 g + m), cv [maxB, kv_heads, M, vdim];
   // parallel layers with a convolution: conv_tail [maxB, width, taps - 1] the last rows of the layer's normed input
+  // window attention: ck [maxB, kv_heads, M, dim], cv [maxB, kv_heads, M, vdim]; state-space mixer: S [maxB, heads, state, vdim],
+  // conv_tail [maxB, heads vdim + 2 groups state, taps - 1]; gated linear attention: S
+  LLState* pair = nullptr;            // state of the layer's second mixer
 };
 
 struct LLRun {
@@ -72,6 +85,12 @@ struct LayerList {
   std::vector<LLRun> runs;       // execution order
   std::vector<LLState> state;    // per run
   float* loop_step = nullptr;    // [loop_times, width] fp32
+  void* loop_in = nullptr;       // [width, 2 width] of WT: the looped block's entry projection (loop_in)
+  float* embed_norm = nullptr;   // [width]
+  float *x0 = nullptr, *cat = nullptr;  // the embedding output [cap_tok, width]; [x | x0] rows [cap_tok, 2 width]
+  void* cat16 = nullptr;
+  float *win_part_o = nullptr, *win_part_ml = nullptr;  // split scratch of the window attention
+  float* xs = nullptr;           // state-space mixer: the convolved x [cap_tok, heads * vdim]
   void* side_embed = nullptr;  // [vocab, n_layers * side_dim] of WT
   std::set<std::string> loaded;
   std::vector<int> slot_pos;   // next position of every sequence slot (host copy)

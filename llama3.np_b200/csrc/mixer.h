@@ -48,7 +48,7 @@ cudaError_t launch_delta_prep(const DeltaPrepArgs& a, int rows, cudaStream_t s);
 cudaError_t launch_conv_tail(float* tail, const float* proj, int ld, int B, int L, int C, int T1, cudaStream_t s);
 // out[r] = x[src_rows ? src_rows[r] : r * src_mul + src_add] / rms * w  (+ bf16 mirror); any D
 cudaError_t launch_rmsnorm_rows(const float* x, const float* w, float eps, int rows, int D, int src_mul, int src_add,
-                                const int32_t* src_rows, float* out, bf16* out16, cudaStream_t s);
+                                const int32_t* src_rows, float* out, bf16* out16, cudaStream_t s, int groups = 1);
 cudaError_t launch_to_bf16(const float* in, int64_t n, bf16* out, cudaStream_t s);
 cudaError_t launch_add_one(float* p, int n, cudaStream_t s);
 
@@ -56,11 +56,13 @@ cudaError_t launch_add_one(float* p, int n, cudaStream_t s);
 struct RecurArgs {
   int mode;               // 0: S <- decay_h S + k v^T, o = S^T q  (q, k, v read through silu when act_in)
                           // 1: S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q
+                          // 2: S <- diag(g) S + k v^T; o = S^T q
   const float *q, *k, *v; // rows [B * L, ld_*]; head h of q / k at column (h / rep) * DK, of v at column h * DV
   int ld_q, ld_k, ld_v;
   int act_in;             // silu on q, k, v as they are read: 0 no, 1 exact form, 2 fast exponential and divide (pipelined kernel)
   const float* head_decay;  // mode 0: [H]
-  const float* g;         // mode 1: [B * L, H * DK]
+  const float* g;         // mode 1, 2: [B * L, H * DK]; with g_head [B * L, H], one decay for all key channels of a head
+  int g_head;
   const float* beta;      // mode 1: [B * L, H]
   float* state;           // [maxB, H, DK, DV]
   float* out;             // [B * L, H * DV]
@@ -83,8 +85,9 @@ cudaError_t launch_attn_any(const AttnArgs& a, bool kv_bf16, cudaStream_t s);
 // out[r] = n(x[r]) + (prev - n(x[r])) * shift with n(v) = v / rms(v) * w (w: D weights) and prev = n(x[r - 1]) inside a
 // sequence, hprev[b] for its first token; the CTA of a sequence's first token then stores n(x[last row]) to hprev[b].
 // shift == null: plain norm.  out16 (may be null): bf16 mirror.
+// groups > 1: the norm cuts a row into that many equal consecutive parts, each over its own root mean square
 cudaError_t launch_prenorm_shift(const float* x, const float* w, float eps, const float* shift, float* hprev, int B, int L,
-                                 int D, float* out, bf16* out16, cudaStream_t s);
+                                 int D, float* out, bf16* out16, cudaStream_t s, int groups = 1);
 // x[r, i] = x[r, i] * mul + (vec ? vec[i] : 0)
 cudaError_t launch_scale_add_rows(float* x, float mul, const float* vec, int rows, int D, cudaStream_t s);
 
@@ -235,3 +238,78 @@ cudaError_t launch_moe_glu_act(const float* gu, const float* dense, int rows, in
 cudaError_t launch_moe_glu_rows(const float* h, const void* w_gu, const void* w_down, bool w_bf16, const int32_t* sel,
                                 const float* w, int rows, int D, int E, int ff, int sff, int top, float* hid, float* y,
                                 cudaStream_t s);
+
+// ---- sliding-window attention with kept first tokens, sink softmax or sigmoid weights (attn_window.cu)
+struct WinPrepArgs {
+  const float* proj;     // [rows, ld]: q (H x DK) at q_off, k (G x DK) at k_off, v (G x DV) at v_off
+  int ld, q_off, k_off, v_off;
+  const float* inv_freq; // [rot_dims / 2]
+  int rot_dims, rot_layout;  // layout 0: entries (2i, 2i + 1) turn together; 1: entries (i, i + rot_dims / 2)
+  int unit_norm;         // 1: q and k over their root mean square per head, after the rotation
+  float eps;
+  float* q_out;          // [rows, H, DK]
+  void* cache_k;         // [maxB, G, M, DK] of KVT
+  void* cache_v;         // [maxB, G, M, DV]
+  const int* pos_ptr;
+  int L, H, G, DK, DV, M;
+};
+cudaError_t launch_win_prep(const WinPrepArgs& a, int rows, bool kv_bf16, cudaStream_t s);
+struct WinAttnArgs {
+  const float* q;        // [B * L, H, DK]
+  const void* cache_k;   // [maxB, G, M, DK]
+  const void* cache_v;   // [maxB, G, M, DV]
+  float* out;            // out[r * ld_out + h * DV + d] (+ bf16 mirror, may be null), times out_scale
+  bf16* out16;
+  int ld_out;
+  float out_scale;
+  const float* head_vec; // [H]: the sink's logit (softmax; null: no sink) or the bias inside the sigmoid
+  const int* pos_ptr;    // token t of the call sits at *pos_ptr + t
+  float scale;
+  int kind;              // L3_ATTN_SINK | L3_ATTN_SIGMOID
+  int window, keep_first;  // query i sees key j <= i with i - j < window (0: all) or j < keep_first
+  int B, L, H, G, DK, DV, M;
+  int nsplit;            // > 1: the key tiles of a query spread over that many CTAs; partials in part_o / part_ml
+  float *part_o, *part_ml;
+};
+bool win_attn_supported(int DK, int DV);
+int win_attn_splits(int B, int L, int H, int G, int window, int keep_first, int max_keys, int max_split);
+size_t win_attn_part_floats(int max_rows, int H, int DV, int max_split);
+cudaError_t launch_win_attn(const WinAttnArgs& a, bool kv_bf16, cudaStream_t s);
+
+// ---- state-space and gated-linear mixers, output stage, small row kernels (hybrid_ops.cu)
+struct SsdPrepArgs {
+  const float* proj;      // [rows, ld]: x | B | C channels (H DV + 2 G N) at xbc_off, dt logits (H) at dt_off
+  int ld, xbc_off, dt_off;
+  const float* conv_w;    // [C, taps], last tap = current token
+  const float* conv_b;    // [C]
+  const float* conv_tail; // [maxB, C, taps - 1]
+  const float* A_log;     // [H]
+  const float* dt_bias;   // [H]
+  float* x_out;           // [rows, H * DV] convolved x (the skip term reads it)
+  float* v_out;           // [rows, H * DV] dt * x
+  float *k_out, *q_out;   // [rows, G * N] B and C
+  float* decay_out;       // [rows, H] exp(-exp(A_log) dt)
+  int L, H, G, N, DV, taps;
+};
+cudaError_t launch_ssd_prep(const SsdPrepArgs& a, int rows, cudaStream_t s);
+// q_out[r, i] = q[r * ld + i] * q_mul;  g_out[r, i] = sigmoid(z[r * ld_z + i] + bias[i])^(1 / tau)   (i < n)
+cudaError_t launch_gla_prep(const float* q, int ld, float q_mul, const float* z, int ld_z, const float* bias, float tau, int rows,
+                            int n, float* q_out, float* g_out, cudaStream_t s);
+// Output stage of a recurrent mixer, a CTA per row of n = H * DV values:
+//   y = o + skip_d[i / DV] * skip_x[r, i]                       (skip_d null: y = o)
+//   pre_gate 1:  y <- y * act(gate), then out = y / rms_group(y) * w[i % wlen]
+//   pre_gate 0:  out = y / rms_group(y) * w[i % wlen] * act(gate)
+// with groups of `group` consecutive values, act = sigmoid (gate_act 0) or silu (1); out[r * ld_out + i] * out_scale
+struct MixOutArgs {
+  const float* o; int n;
+  const float* skip_d; const float* skip_x; int DV;
+  const float* gate; int ld_gate; int gate_act, pre_gate;
+  const float* w; int wlen, group;
+  float eps, out_scale;
+  float* out; bf16* out16; int ld_out;
+};
+cudaError_t launch_mix_out(const MixOutArgs& a, int rows, cudaStream_t s);
+// x <- cap * tanh(x / cap), n values
+cudaError_t launch_softcap(float* x, int64_t n, float cap, cudaStream_t s);
+// out[r] = [a[r] | b[r]] (D values each; + bf16 mirror)
+cudaError_t launch_concat_rows(const float* a, const float* b, int rows, int D, float* out, bf16* out16, cudaStream_t s);

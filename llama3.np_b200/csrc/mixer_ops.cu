@@ -188,20 +188,27 @@ __global__ void conv_tail_kernel(float* __restrict__ tail, const float* __restri
   }
 }
 
-// out[r] = x[source row of r] / rms * w, any D; source row = src_rows[r] or r * src_mul + src_add
+// out[r] = x[source row of r] / rms * w, any D; source row = src_rows[r] or r * src_mul + src_add; groups > 1: the row is
+// cut into that many equal parts, each over its own root mean square
 __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps,
                                                            int D, int src_mul, int src_add, const int32_t* __restrict__ src_rows,
-                                                           float* __restrict__ out, bf16* __restrict__ out16) {
+                                                           int groups, float* __restrict__ out, bf16* __restrict__ out16) {
   __shared__ float red[32];
+  __shared__ float rg[32];
   pdl_launch();
   pdl_wait();
   const size_t r = blockIdx.x;
   const float* xr = x + (src_rows ? (size_t)src_rows[r] : r * src_mul + src_add) * D;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < D; i += blockDim.x) { const float v = xr[i]; ss = fmaf(v, v, ss); }
-  const float rinv = 1.0f / sqrtf(block_sum(ss, red) / (float)D + eps);
+  const int gs = D / groups;
+  for (int g = 0; g < groups; ++g) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) { const float v = xr[g * gs + i]; ss = fmaf(v, v, ss); }
+    const float tot = block_sum(ss, red);
+    if (threadIdx.x == 0) rg[g] = 1.0f / sqrtf(tot / (float)gs + eps);
+  }
+  __syncthreads();
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
-    const float v = xr[i] * rinv * w[i];
+    const float v = xr[i] * rg[i / gs] * w[i];
     out[r * D + i] = v;
     if (out16) out16[r * D + i] = __float2bfloat16_rn(v);
   }
@@ -265,8 +272,9 @@ cudaError_t launch_conv_tail(float* tail, const float* proj, int ld, int B, int 
 }
 
 cudaError_t launch_rmsnorm_rows(const float* x, const float* w, float eps, int rows, int D, int src_mul, int src_add,
-                                const int32_t* src_rows, float* out, bf16* out16, cudaStream_t s) {
-  return launch_k(rmsnorm_rows_kernel, dim3(rows), dim3(row_threads(D)), 0, s, x, w, eps, D, src_mul, src_add, src_rows, out, out16);
+                                const int32_t* src_rows, float* out, bf16* out16, cudaStream_t s, int groups) {
+  if (groups < 1 || groups > 32 || D % groups != 0) return cudaErrorInvalidValue;
+  return launch_k(rmsnorm_rows_kernel, dim3(rows), dim3(row_threads(D)), 0, s, x, w, eps, D, src_mul, src_add, src_rows, groups, out, out16);
 }
 
 cudaError_t launch_to_bf16(const float* in, int64_t n, bf16* out, cudaStream_t s) {

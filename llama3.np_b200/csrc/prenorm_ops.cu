@@ -25,43 +25,54 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return t;
 }
 
-__device__ __forceinline__ float row_rinv(const float* __restrict__ row, int D, float eps, float* red) {
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < D; i += blockDim.x) { const float v = row[i]; ss = fmaf(v, v, ss); }
-  return 1.0f / sqrtf(block_sum(ss, red) / (float)D + eps);
+// 1 / rms of every one of `groups` equal consecutive parts of a row, into out[groups] (shared memory)
+__device__ __forceinline__ void row_rinv(const float* __restrict__ row, int D, int groups, float eps, float* red, float* out) {
+  const int gs = D / groups;
+  for (int g = 0; g < groups; ++g) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) { const float v = row[g * gs + i]; ss = fmaf(v, v, ss); }
+    const float tot = block_sum(ss, red);
+    if (threadIdx.x == 0) out[g] = 1.0f / sqrtf(tot / (float)gs + eps);
+  }
+  __syncthreads();
 }
+
+constexpr int NORM_GROUPS_MAX = 32;
 
 __global__ void __launch_bounds__(256) prenorm_shift_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps,
                                                             const float* __restrict__ shift, float* __restrict__ hprev, int L,
-                                                            int D, float* __restrict__ out, bf16* __restrict__ out16) {
+                                                            int D, int groups, float* __restrict__ out, bf16* __restrict__ out16) {
   __shared__ float red[32];
+  __shared__ float rc[NORM_GROUPS_MAX], rp[NORM_GROUPS_MAX], rl[NORM_GROUPS_MAX];
   pdl_launch();
   pdl_wait();
   const size_t r = blockIdx.x;
   const int b = (int)(r / L), t = (int)(r - (size_t)b * L);
+  const int gs = D / groups;
   const float* xr = x + r * D;
-  const float rc = row_rinv(xr, D, eps, red);
+  row_rinv(xr, D, groups, eps, red, rc);
   if (!shift) {
     for (int i = threadIdx.x; i < D; i += blockDim.x) {
-      const float h = xr[i] * rc * w[i];
+      const float h = xr[i] * rc[i / gs] * w[i];
       out[r * D + i] = h;
       if (out16) out16[r * D + i] = __float2bfloat16_rn(h);
     }
     return;
   }
   const float* xp = xr - D;  // previous token of the same sequence (t > 0)
-  const float rp = t > 0 ? row_rinv(xp, D, eps, red) : 0.f;
+  if (t > 0) row_rinv(xp, D, groups, eps, red, rp);
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
-    const float h = xr[i] * rc * w[i];
-    const float prev = t > 0 ? xp[i] * rp * w[i] : hprev[(size_t)b * D + i];
+    const float h = xr[i] * rc[i / gs] * w[i];
+    const float prev = t > 0 ? xp[i] * rp[i / gs] * w[i] : hprev[(size_t)b * D + i];
     const float v = h + (prev - h) * shift[i];
     out[r * D + i] = v;
     if (out16) out16[r * D + i] = __float2bfloat16_rn(v);
   }
   if (t == 0) {  // this CTA alone touches hprev[b]: read above, replaced here
     const float* xl = xr + (size_t)(L - 1) * D;
-    const float rl = L > 1 ? row_rinv(xl, D, eps, red) : rc;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) hprev[(size_t)b * D + i] = xl[i] * rl * w[i];
+    __syncthreads();  // every thread has read its hprev entries
+    row_rinv(xl, D, groups, eps, red, rl);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) hprev[(size_t)b * D + i] = xl[i] * rl[i / gs] * w[i];
   }
 }
 
@@ -179,8 +190,9 @@ int row_threads(int D) { return D >= 1024 ? 256 : D >= 256 ? 128 : 64; }
 }  // namespace
 
 cudaError_t launch_prenorm_shift(const float* x, const float* w, float eps, const float* shift, float* hprev, int B, int L,
-                                 int D, float* out, bf16* out16, cudaStream_t s) {
-  return launch_k(prenorm_shift_kernel, dim3(B * L), dim3(row_threads(D)), 0, s, x, w, eps, shift, hprev, L, D, out, out16);
+                                 int D, float* out, bf16* out16, cudaStream_t s, int groups) {
+  if (groups < 1 || groups > NORM_GROUPS_MAX || D % groups != 0) return cudaErrorInvalidValue;
+  return launch_k(prenorm_shift_kernel, dim3(B * L), dim3(row_threads(D)), 0, s, x, w, eps, shift, hprev, L, D, groups, out, out16);
 }
 
 cudaError_t launch_scale_add_rows(float* x, float mul, const float* vec, int rows, int D, cudaStream_t s) {

@@ -4,6 +4,7 @@
 //
 //   mode 0   S <- decay_h S + k v^T                                   o = S^T q
 //   mode 1   S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T    o = S^T q   (o sees this token's write)
+//   mode 2   S <- diag(g) S + k v^T                                   o = S^T q   (g per key channel, or one per head)
 //
 // The columns of S never mix: column j needs v_j, the token's k, q, g (shared by all columns) and nothing of
 // any other column.  So a CTA owns a tile of CPB columns of one (slot, head) for the whole call; a column is
@@ -28,8 +29,8 @@ __global__ void __launch_bounds__(256) recur_kernel(RecurArgs a, int TPC, int CP
   const int DKP = R * TPC;  // padded key dimension: rows >= DK hold zeros
   float* sq = sm;                                   // [TCH][DKP]
   float* sk = sq + (size_t)TCH * DKP;               // [TCH][DKP]
-  float* sg = sk + (size_t)TCH * DKP;               // [TCH][DKP]   (mode 1)
-  float* sv = sg + (MODE == 1 ? (size_t)TCH * DKP : 0);  // [TCH][CPB]
+  float* sg = sk + (size_t)TCH * DKP;               // [TCH][DKP]   (modes 1, 2)
+  float* sv = sg + (MODE >= 1 ? (size_t)TCH * DKP : 0);  // [TCH][CPB]
   float* so = sv + (size_t)TCH * CPB;               // [TCH][CPB]
   float* sb = so + (size_t)TCH * CPB;               // [TCH]        (mode 1)
   pdl_launch();
@@ -62,11 +63,11 @@ __global__ void __launch_bounds__(256) recur_kernel(RecurArgs a, int TPC, int CP
         qv = a.q[row * a.ld_q + (size_t)kvh * a.DK + i];
         kv = a.k[row * a.ld_k + (size_t)kvh * a.DK + i];
         if (a.act_in) { qv = silu_ref(qv); kv = silu_ref(kv); }
-        if (MODE == 1) gv = a.g[row * ((size_t)a.H * a.DK) + (size_t)h * a.DK + i];
+        if (MODE >= 1) gv = a.g_head ? a.g[row * (size_t)a.H + h] : a.g[row * ((size_t)a.H * a.DK) + (size_t)h * a.DK + i];
       }
       sq[idx] = qv;
       sk[idx] = kv;
-      if (MODE == 1) sg[idx] = gv;
+      if (MODE >= 1) sg[idx] = gv;
     }
     for (int idx = tid; idx < n * CPB; idx += nthr) {
       const int tok = idx / CPB, c = idx - tok * CPB;
@@ -91,6 +92,13 @@ __global__ void __launch_bounds__(256) recur_kernel(RecurArgs a, int TPC, int CP
 #pragma unroll
         for (int r = 0; r < R; ++r) {
           S[r] = fmaf(lam, S[r], kk[r * TPC] * vj);
+          acc = fmaf(S[r], qk[r * TPC], acc);
+        }
+      } else if (MODE == 2) {
+        const float* gk = sg + (size_t)tok * DKP + s;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          S[r] = fmaf(gk[r * TPC], S[r], kk[r * TPC] * vj);
           acc = fmaf(S[r], qk[r * TPC], acc);
         }
       } else {
@@ -141,7 +149,7 @@ constexpr int RP_TCH = 16;
 template <int TPC, int MODE>
 __global__ void __launch_bounds__(256) recur_pipe_kernel(RecurArgs a) {
   constexpr int R = 8, DKP = R * TPC, CPB = 256 / TPC, TCH = RP_TCH;
-  constexpr int NA = MODE == 1 ? 3 : 2;               // staged operand arrays of DKP floats per token: q, k (, g)
+  constexpr int NA = MODE >= 1 ? 3 : 2;               // staged operand arrays of DKP floats per token: q, k (, g)
   constexpr int NPF = TCH * DKP / 256;                // floats per thread and array in the register stage
   constexpr int NV = (TCH * CPB + 255) / 256;
   constexpr int BUF = TCH * (NA * DKP + CPB) + TCH;   // floats per buffer: q | k | (g) | v | beta
@@ -167,7 +175,7 @@ __global__ void __launch_bounds__(256) recur_pipe_kernel(RecurArgs a) {
   const float lam = MODE == 0 ? a.head_decay[h] : 0.f;
   const size_t row0 = (size_t)b * a.L;
 
-  float pq[NPF], pk[NPF], pg[MODE == 1 ? NPF : 1], pv[NV], pb = 0.f;
+  float pq[NPF], pk[NPF], pg[MODE >= 1 ? NPF : 1], pv[NV], pb = 0.f;
   // A thread's share of a chunk: operand element i_f of tokens tok_f, tok_f + TSTEP, ... (DKP divides 256, so i_f never
   // changes) and value column c_f of tokens tok_v, tok_v + VSTEP, ...: the addresses advance by a constant per load.
   constexpr int TSTEP = 256 / DKP, VSTEP = CPB >= 256 ? 1 : 256 / CPB;
@@ -175,19 +183,21 @@ __global__ void __launch_bounds__(256) recur_pipe_kernel(RecurArgs a) {
   const bool i_ok = i_f < a.DK, c_ok = tile * CPB + c_f < a.DV;
   const float* q_f = a.q + (row0 + tok_f) * a.ld_q + (size_t)kvh * a.DK + i_f;
   const float* k_f = a.k + (row0 + tok_f) * a.ld_k + (size_t)kvh * a.DK + i_f;
-  const float* g_f = MODE == 1 ? a.g + (row0 + tok_f) * ((size_t)a.H * a.DK) + (size_t)h * a.DK + i_f : nullptr;
+  // the decays: one per (head, key channel), or with g_head one per head
+  const size_t g_row = a.g_head ? (size_t)a.H : (size_t)a.H * a.DK;
+  const float* g_f = MODE >= 1 ? a.g + (row0 + tok_f) * g_row + (a.g_head ? (size_t)h : (size_t)h * a.DK + i_f) : nullptr;
   const float* v_f = a.v + (row0 + tok_v) * a.ld_v + (size_t)h * a.DV + tile * CPB + c_f;
-  const size_t q_st = (size_t)TSTEP * a.ld_q, k_st = (size_t)TSTEP * a.ld_k, g_st = (size_t)TSTEP * a.H * a.DK, v_st = (size_t)VSTEP * a.ld_v;
+  const size_t q_st = (size_t)TSTEP * a.ld_q, k_st = (size_t)TSTEP * a.ld_k, g_st = (size_t)TSTEP * g_row, v_st = (size_t)VSTEP * a.ld_v;
   auto fetch = [&](int t0) {  // global -> registers, tokens [t0, t0 + TCH) clipped to L
     const float* qp = q_f + (size_t)t0 * a.ld_q;
     const float* kp = k_f + (size_t)t0 * a.ld_k;
-    const float* gp = MODE == 1 ? g_f + (size_t)t0 * a.H * a.DK : nullptr;
+    const float* gp = MODE >= 1 ? g_f + (size_t)t0 * g_row : nullptr;
 #pragma unroll
     for (int n = 0; n < NPF; ++n) {
       const bool ok = i_ok && t0 + tok_f + n * TSTEP < a.L;
       pq[n] = ok ? qp[n * q_st] : 0.f;
       pk[n] = ok ? kp[n * k_st] : 0.f;
-      if (MODE == 1) pg[n] = ok ? gp[n * g_st] : 0.f;
+      if (MODE >= 1) pg[n] = ok ? gp[n * g_st] : 0.f;
     }
     const float* vp = v_f + (size_t)t0 * a.ld_v;
 #pragma unroll
@@ -206,7 +216,7 @@ __global__ void __launch_bounds__(256) recur_pipe_kernel(RecurArgs a) {
       const int e = tid + n * 256;
       buf[e] = a.act_in ? act(pq[n]) : pq[n];
       buf[TCH * DKP + e] = a.act_in ? act(pk[n]) : pk[n];
-      if (MODE == 1) buf[2 * TCH * DKP + e] = pg[n];
+      if (MODE >= 1) buf[2 * TCH * DKP + e] = pg[n];
     }
 #pragma unroll
     for (int n = 0; n < NV; ++n) {
@@ -284,6 +294,16 @@ __global__ void __launch_bounds__(256) recur_pipe_kernel(RecurArgs a) {
           acc0 = fmaf(S[r], qr[r], acc0);
           acc1 = fmaf(S[r + 4], qr[r + 4], acc1);
         }
+      } else if (MODE == 2) {
+        const float4 ga = g4[o4], gb = g4[o4 + TPC];
+        const float gr[R] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          S[r] = fmaf(gr[r], S[r], kr[r] * vj);
+          S[r + 4] = fmaf(gr[r + 4], S[r + 4], kr[r + 4] * vj);
+          acc0 = fmaf(S[r], qr[r], acc0);
+          acc1 = fmaf(S[r + 4], qr[r + 4], acc1);
+        }
       } else {
         const float4 ga = g4[o4], gb = g4[o4 + TPC];
         const float gr[R] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
@@ -331,7 +351,7 @@ __global__ void __launch_bounds__(256) recur_pipe_kernel(RecurArgs a) {
 template <int TPC>
 cudaError_t launch_recur_pipe(const RecurArgs& a, cudaStream_t s) {
   constexpr int DKP = 8 * TPC, CPB = 256 / TPC;
-  const int NA = a.mode == 1 ? 3 : 2;
+  const int NA = a.mode >= 1 ? 3 : 2;
   const size_t smem = (size_t)(2 * (RP_TCH * (NA * DKP + CPB) + RP_TCH) + RP_TCH * CPB) * sizeof(float);
   const dim3 grid(a.H * ((a.DV + CPB - 1) / CPB), a.B);
   auto go = [&](auto kern) {
@@ -341,7 +361,7 @@ cudaError_t launch_recur_pipe(const RecurArgs& a, cudaStream_t s) {
     }
     return launch_k(kern, grid, dim3(256), smem, s, a);
   };
-  return a.mode == 0 ? go(recur_pipe_kernel<TPC, 0>) : go(recur_pipe_kernel<TPC, 1>);
+  return a.mode == 0 ? go(recur_pipe_kernel<TPC, 0>) : a.mode == 1 ? go(recur_pipe_kernel<TPC, 1>) : go(recur_pipe_kernel<TPC, 2>);
 }
 
 int pow2_at_least(int v) {
@@ -356,12 +376,13 @@ cudaError_t launch_recur_r(const RecurArgs& a, cudaStream_t s) {
   const int CPB = std::max(1, std::min(256 / TPC, pow2_at_least(a.DV)));
   const int threads = std::max(32, CPB * TPC);  // CPB * TPC is a power of two: whole warps once it reaches 32
   const int DKP = R * TPC;
-  const int per_tok = (a.mode == 1 ? 3 : 2) * DKP + 2 * CPB + 1;
+  const int per_tok = (a.mode >= 1 ? 3 : 2) * DKP + 2 * CPB + 1;
   const int TCH = std::max(1, std::min(32, 11000 / per_tok));
   const size_t smem = (size_t)TCH * per_tok * sizeof(float);
   const int ntile = (a.DV + CPB - 1) / CPB;
   const dim3 grid(a.H * ntile, a.B);
   if (a.mode == 0) return launch_k(recur_kernel<R, 0>, grid, dim3(threads), smem, s, a, TPC, CPB, TCH);
+  if (a.mode == 2) return launch_k(recur_kernel<R, 2>, grid, dim3(threads), smem, s, a, TPC, CPB, TCH);
   return launch_k(recur_kernel<R, 1>, grid, dim3(threads), smem, s, a, TPC, CPB, TCH);
 }
 

@@ -43,7 +43,14 @@ def _mabedra(model_dir, config, *, dtype, max_seq_len, max_batch_size, device):
                    max_seq_len=max_seq_len or 256, max_batch_size=max_batch_size, device=device)
 
 
-ARCHITECTURES = {"Llama": _llama, "Risalix": _risalix, "Rakelorn": _rakelorn, "Mabedra": _mabedra}
+def _debuzen(model_dir, config, *, dtype, max_seq_len, max_batch_size, device):
+    from .debuzen import Debuzen
+    from .utils import read_safetensors
+    return Debuzen(config, read_safetensors(os.path.join(model_dir, "model.safetensors")), dtype=dtype,
+                   max_seq_len=max_seq_len or 256, max_batch_size=max_batch_size, device=device)
+
+
+ARCHITECTURES = {"Llama": _llama, "Risalix": _risalix, "Rakelorn": _rakelorn, "Mabedra": _mabedra, "Debuzen": _debuzen}
 
 
 def load_model(model_dir, *, dtype: str = "float32", max_seq_len: int = 0, max_batch_size: int = 1, device: int = 0):

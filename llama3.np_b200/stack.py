@@ -19,6 +19,8 @@ from . import _cabi
 
 SOFTMAX, DECAY_LINEAR, GATED_DELTA = _cabi.MIX_SOFTMAX, _cabi.MIX_DECAY_LINEAR, _cabi.MIX_GATED_DELTA
 LATENT, MINGRU, DIFF = _cabi.MIX_LATENT, _cabi.MIX_MINGRU, _cabi.MIX_DIFF
+WINDOW, SSD, GLA = _cabi.MIX_WINDOW, _cabi.MIX_SSD, _cabi.MIX_GLA
+ATTN_SINK, ATTN_SIGMOID = _cabi.ATTN_SINK, _cabi.ATTN_SIGMOID
 FF_GLU, FF_POLYNORM = _cabi.FF_GLU, _cabi.FF_POLYNORM
 ROUTE_SOFTMAX, ROUTE_SIGMOID_IN = _cabi.ROUTE_SOFTMAX, _cabi.ROUTE_SIGMOID_IN
 _DTYPES = {"float32": _cabi.DTYPE_F32, "fp32": _cabi.DTYPE_F32, "bfloat16": _cabi.DTYPE_BF16, "bf16": _cabi.DTYPE_BF16}
@@ -54,6 +56,15 @@ class LayerSpec:
     ff_kind: int = 0              # FF_GLU | FF_POLYNORM
     router_kind: int = 0          # ROUTE_SOFTMAX | ROUTE_SIGMOID_IN
     shared_ff: int = 0            # ROUTE_SIGMOID_IN: width of the shared expert
+    keep_first: int = 0           # WINDOW: the first tokens that stay visible behind the window
+    attn_kind: int = 0            # WINDOW: ATTN_SINK (softmax with a sink per head) | ATTN_SIGMOID (sigmoid(score + bias), not normalised)
+    rot_layout: int = 0           # WINDOW: 0 = entries (2i, 2i + 1) turn together, 1 = entries (i, i + rot_dims / 2)
+    qk_unit: bool = False         # WINDOW: q and k over their root mean square per head, after the rotation
+    out_norm_groups: int = 1      # SSD: parts of the output norm
+    tau: float = 1.0              # GLA: the decay is sigmoid(.)^(1 / tau)
+    pair: Optional["LayerSpec"] = None   # a second mixer on the same input (tensors mix.left.* / mix.right.*)
+    mix_scale: float = 1.0        # with `pair`: result = mix_scale * mixer + pair_scale * pair mixer
+    pair_scale: float = 1.0
 
 
 @dataclass
@@ -76,6 +87,10 @@ class StackConfig:
     layer_scale: bool = False     # per-channel multipliers l<i>.ls1 / ls2 on the sublayers' results
     canon_taps: int = 0           # taps of the causal convolution ahead of every sublayer; 0 = none
     depth_avg: bool = False       # the stream handed on is a weighted sum of every earlier layer's result
+    norm_groups: int = 1          # pre-norm stacks: every norm cuts the vector into this many parts, each over its own RMS
+    embed_norm: bool = False      # the embedding rows pass a norm (tensor embed.norm)
+    loop_in: bool = False         # ahead of every pass of the loop x <- W [x ; x0] (tensor loop.in) instead of x + loop.step[pass]
+    logit_softcap: float = 0.0    # c > 0: logits <- c tanh(logits / c)
     max_seq_len: int = 256
     max_batch_size: int = 1
     dtype: str = "float32"
@@ -93,12 +108,17 @@ class StackDecoder:
         self._finalized = False
         specs = (_cabi.L3LayerSpec * len(cfg.layers))()
         keep = []
-        for i, l in enumerate(cfg.layers):
+
+        def c_spec(i, l):
             dec = (C.c_float * max(1, len(l.decay)))(*[float(x) for x in l.decay])
             keep.append(dec)
             if l.mixer == DECAY_LINEAR and len(l.decay) != l.heads:
                 raise ValueError(f"layer {i}: {len(l.decay)} decays for {l.heads} heads")
-            specs[i] = _cabi.L3LayerSpec(mixer=l.mixer, heads=l.heads, kv_heads=l.kv_heads or l.heads, dim=l.dim, vdim=l.vdim,
+            pair = None
+            if l.pair is not None:
+                pair = c_spec(i, l.pair)
+                keep.append(pair)
+            return _cabi.L3LayerSpec(mixer=l.mixer, heads=l.heads, kv_heads=l.kv_heads or l.heads, dim=l.dim, vdim=l.vdim,
                                          conv_taps=l.conv_taps, rank_decay=l.rank_decay, rank_gate=l.rank_gate, ff=l.ff,
                                          scale=l.scale, decay=C.cast(dec, C.POINTER(C.c_float)) if len(l.decay) else None,
                                          q_rank=l.q_rank, kv_rank=l.kv_rank, rot_dim=l.rot_dim, rot_dims=l.rot_dims,
@@ -109,7 +129,14 @@ class StackDecoder:
                                          rot_scale_low=float(l.rot_scaling[1]) if l.rot_scaling else 0.0,
                                          rot_scale_high=float(l.rot_scaling[2]) if l.rot_scaling else 0.0,
                                          rot_scale_original=int(l.rot_scaling[3]) if l.rot_scaling else 0,
-                                         ff_kind=l.ff_kind, router_kind=l.router_kind, shared_ff=l.shared_ff)
+                                         ff_kind=l.ff_kind, router_kind=l.router_kind, shared_ff=l.shared_ff,
+                                         keep_first=l.keep_first, attn_kind=l.attn_kind, rot_layout=l.rot_layout,
+                                         qk_unit=int(l.qk_unit), out_norm_groups=l.out_norm_groups, tau=float(l.tau),
+                                         pair=C.pointer(pair) if pair is not None else None,
+                                         mix_scale=float(l.mix_scale), pair_scale=float(l.pair_scale))
+
+        for i, l in enumerate(cfg.layers):
+            specs[i] = c_spec(i, l)
         c = _cabi.L3StackConfig(width=cfg.width, vocab=cfg.vocab, n_layers=len(cfg.layers), max_seq_len=cfg.max_seq_len,
                                 max_batch_size=cfg.max_batch_size, dtype=_DTYPES[cfg.dtype], device=device, flags=flags,
                                 norm_eps=cfg.norm_eps, residual_mult=cfg.residual_mult, norm_one_plus=int(cfg.norm_one_plus),
@@ -119,7 +146,8 @@ class StackDecoder:
                                 loop_start=cfg.loop[0] if cfg.loop else 0, loop_stop=cfg.loop[1] if cfg.loop else 0,
                                 loop_times=cfg.loop[2] if cfg.loop else 0, parallel=int(cfg.parallel),
                                 norm_center=int(cfg.norm_center), layer_scale=int(cfg.layer_scale),
-                                canon_taps=int(cfg.canon_taps), depth_avg=int(cfg.depth_avg))
+                                canon_taps=int(cfg.canon_taps), depth_avg=int(cfg.depth_avg), norm_groups=int(cfg.norm_groups),
+                                embed_norm=int(cfg.embed_norm), loop_in=int(cfg.loop_in), logit_softcap=float(cfg.logit_softcap))
         _cabi.check(self._lib.l3_create_stack(C.byref(c), specs, C.byref(self._h)))
         n = C.c_int()
         _cabi.check(self._lib.l3_stack_runs(self._h, C.byref(n)), self._h)
