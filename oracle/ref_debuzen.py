@@ -348,4 +348,7 @@ def random_tensors(config, seed=0, scale=1.0):
             t[q + "q"], t[q + "k"], t[q + "v"], t[q + "g"] = mat(H * dk, W, 2.0), mat(H * dk, W, 2.0), mat(H * dv, W), mat(H * dv, W)
             t[q + "a1"], t[q + "a2"], t[q + "a2.b"] = mat(ra, W), mat(H * dk, ra, 2.0), vec(H * dk, 2.0, 1.0)
             t[q + "norm"], t[q + "o"] = vec(dv, 1.0, 0.1), mat(W, H * dv)
+    # values a bfloat16 checkpoint can hold exactly
+    for k in t:
+        t[k] = (np.ascontiguousarray(t[k], np.float32).view(np.uint32) & np.uint32(0xFFFF0000)).view(np.float32)
     return t
