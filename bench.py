@@ -724,9 +724,65 @@ def mabedra_layer_params(cfg):
     return held, read
 
 
+# ------------------------------------------------------------------------------ --arch debuzen
+# Six hybrid pre-norm layers, the first three run twice (9 layer runs per token): sigmoid sliding-window attention (window
+# 1024, 4 kept tokens, GQA 4:1, heads of 128) beside a gated delta rule; sink-softmax sliding-window attention beside a
+# Mamba-2 mixer (inner width = width, heads of 64, state 128); gated linear attention (keys of 128, values of 256); a
+# silu-gated feed-forward of 4 x width in every layer; norms in 4 groups.
+def debuzen_bench_config(width, vocab=32000):
+    heads = max(1, width // 128)
+    kv = max(1, heads // 4)
+    mlp = {"kind": "dense", "ff": 4 * width}
+    a1 = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 0.2, "mask": {"size": 1024, "keep_first": 4},
+          "rot": {"base": 1000000.0, "dims": 64}}
+    a2 = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024},
+          "rot": {"base": 500000.0, "dims": 64}}
+    par = {"type": "parallel", "mlp": mlp,
+           "mixer": {"left": a1, "left_scale": 1.0, "right_scale": 1.0,
+                     "right": {"heads": heads, "kv_heads": heads, "dim": 128, "vdim": 128, "conv": 4, "rank_decay": width // 16,
+                               "rank_gate": width // 16}}}
+    par2 = {"type": "parallel_2", "mlp": mlp,
+            "mixer": {"left": a2, "left_scale": 1.0, "right_scale": 1.0,
+                      "right": {"heads": width // 64, "groups": 2, "state": 128, "vdim": 64, "conv": 4, "norm_groups": 2}}}
+    gla = {"type": "gla", "mlp": mlp, "mixer": {"heads": max(1, width // 256), "dim": 128, "vdim": 256, "tau": 16.0, "rank_decay": 16}}
+    return {"architecture": "Debuzen", "layers": [par, par2, gla, par, par2, gla], "norm": {"eps": 1e-6, "groups": 4},
+            "loop": {"start": 0, "stop": 3, "times": 2}, "logit_softcap": 30.0, "vocab": vocab, "width": width}
+
+
+def debuzen_layer_params(cfg):
+    """(parameters held, parameters a token reads: looped layers once per pass)"""
+    W, held, read = cfg["width"], 0, 0
+    lp = cfg.get("loop") or {"start": 0, "stop": 0, "times": 1}
+    if cfg.get("loop"):
+        held += 2 * W * W
+        read += lp["times"] * 2 * W * W
+
+    def attn(mc):
+        return W * (mc["heads"] * mc["dim"] + mc["kv_heads"] * (mc["dim"] + mc["vdim"])) + W * mc["heads"] * mc["vdim"]
+
+    for i, lc in enumerate(cfg["layers"]):
+        mc = lc["mixer"]
+        if lc["type"] == "parallel":
+            r = mc["right"]
+            H, G, dk, dv = r["heads"], r["kv_heads"], r["dim"], r["vdim"]
+            mix = attn(mc["left"]) + W * (2 * G * dk + H * dv + H + r["rank_decay"] + r["rank_gate"]) + r["rank_decay"] * H * dk + r["rank_gate"] * H * dv + W * H * dv
+        elif lc["type"] == "parallel_2":
+            r = mc["right"]
+            inner = r["heads"] * r["vdim"]
+            mix = attn(mc["left"]) + W * (2 * inner + 2 * r["groups"] * r["state"] + r["heads"]) + W * inner
+        else:
+            H, dk, dv = mc["heads"], mc["dim"], mc["vdim"]
+            mix = W * (2 * H * dk + 2 * H * dv + mc["rank_decay"]) + mc["rank_decay"] * H * dk + W * H * dv
+        n = mix + (3 * W * lc["mlp"]["ff"] if lc["mlp"] else 0)
+        held += n
+        read += n * (lp["times"] if lp["start"] <= i < lp["stop"] else 1)
+    return held, read
+
+
 def run_arch_compare(a):
     import llama3_np_b200  # noqa: F401
     from llama3_np_b200 import Llama, ModelArgs, _cabi
+    from llama3_np_b200.debuzen import Debuzen
     from llama3_np_b200.mabedra import Mabedra
     from llama3_np_b200.rakelorn import Rakelorn
     from llama3_np_b200.risalix import Risalix
@@ -776,15 +832,19 @@ def run_arch_compare(a):
         elif a.arch == "mabedra":
             cfg = mabedra_bench_config(W)
             rp, rp_read = mabedra_layer_params(cfg)
+        elif a.arch == "debuzen":
+            cfg = debuzen_bench_config(W)
+            rp, rp_read = debuzen_layer_params(cfg)
         else:
             cfg = risalix_bench_config(W)
             rp = rp_read = risalix_layer_params(cfg)
         heads, kv, ff = W // 128, max(1, W // 512), 4 * W
         lp1 = W * (heads * 128 + 2 * kv * 128) + W * heads * 128 + 3 * W * ff
-        nl = max(1, round(rp / lp1))
+        # the model beside it holds what a token READS here (a looped layer counts once per pass): equal work per token
+        nl = max(1, round((rp_read if a.arch == "debuzen" else rp) / lp1))
         clock = ClockSampler(0)
         clock.start()
-        r = {"rakelorn": Rakelorn, "mabedra": Mabedra, "risalix": Risalix}[a.arch](cfg, None, dtype=dtype, max_seq_len=M, max_batch_size=8, random_seed=1)
+        r = {"rakelorn": Rakelorn, "mabedra": Mabedra, "risalix": Risalix, "debuzen": Debuzen}[a.arch](cfg, None, dtype=dtype, max_seq_len=M, max_batch_size=8, random_seed=1)
         # the decode leg streams what a token reads (chosen experts, looped layers once per pass), the prefill leg's
         # useful work is the same count per token
         rec_r = measure(r, cfg["vocab"], rp_read + cfg["vocab"] * W, True)
@@ -794,9 +854,18 @@ def run_arch_compare(a):
         l = Llama(None, la, hidden_dim=ff, random_seed=1)
         rec_l = measure(l, cfg["vocab"], nl * lp1 + cfg["vocab"] * W, False)
         l.close()
+        extra = {}
+        if a.arch == "debuzen":  # the closest layer-list family (recurrent and attention layers, dense feed-forward) at equal size
+            per = risalix_layer_params(risalix_bench_config(W, n_layers=6)) / 6.0
+            n_ris = max(6, int(round(rp_read / per / 6.0)) * 6)
+            rcfg = risalix_bench_config(W, n_layers=n_ris)
+            rr = Risalix(rcfg, None, dtype=dtype, max_seq_len=M, max_batch_size=8, random_seed=1)
+            extra["risalix"] = {"layers": n_ris, "params_in_layers": risalix_layer_params(rcfg),
+                                **measure(rr, rcfg["vocab"], risalix_layer_params(rcfg) + rcfg["vocab"] * W, True)}
+            rr.close()
         clk = clock.stop()
         out.append({"size": name, "width": W, a.arch: {"layers": len(cfg["layers"]), "params_in_layers": rp, "params_read_per_token": rp_read, **rec_r},
-                    "llama": {"layers": nl, "params_in_layers": nl * lp1, **rec_l}, "clocks": clk})
+                    "llama": {"layers": nl, "params_in_layers": nl * lp1, **rec_l}, **extra, "clocks": clk})
     print(json.dumps({"metric": f"prefill / decode tokens/s, layer-list decoder ({a.arch.capitalize()}) beside Llama at equal width and size",
                       "dtype": a.dtype, "data": "synthetic", "steps": a.steps, "warmup": a.warmup, "peak_source": how,
                       "peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops}, "sizes": out}))
@@ -813,7 +882,7 @@ def main():
     ap.add_argument("--total-len", type=int, default=256, help="profiling only: shorter generate")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="profiling only: skip the CPU legs")
     ap.add_argument("--no-extra", action="store_true", help="headline only: skip the `extra` / `tp` sub-records")
-    ap.add_argument("--arch", default="", choices=["", "risalix", "rakelorn", "mabedra"],
+    ap.add_argument("--arch", default="", choices=["", "risalix", "rakelorn", "mabedra", "debuzen"],
                     help="instead of the headline: prefill / decode throughput of this decoder family beside Llama at equal size")
     ap.add_argument("--arch-sizes", default="w1024,w2048", help="comma list of " + ",".join(ARCH_SIZES))
     ap.add_argument("--arch-prefill", type=int, default=2048)
