@@ -7,10 +7,11 @@
 //                        sincosf), optional division by the vector's root mean square, q to the query buffer, k and the
 //                        value row to the caches
 //  * win_attn_kernel     a CTA holds 32 query rows of ONE key head - row = (token, query head of the group), token-major,
-//                        so the heads of a group share every key / value tile - and walks the keys the tile can see, 32 at
-//                        a time: first the kept tokens that lie ahead of the window, then the window.  A warp owns 4 rows;
-//                        in the score phase a lane is a key (16-byte shared loads, key rows padded by 4 floats), in the
-//                        output phase a lane owns value columns lane, lane + 32, ...  Softmax rows run the online form,
+//                        so the heads of a group share every key / value tile - and walks the keys the tile can see, 64 at
+//                        a time: first the kept tokens that lie ahead of the window, then the window.  A
+//                        warp owns 4 rows; in the score phase a lane holds two keys (16-byte shared loads, key rows padded by
+//                        4 floats), in the output phase a lane owns value columns read as 16-byte pieces while the weights
+//                        arrive as 16-byte broadcasts.  Softmax rows run the online form,
 //                        started at (max = sink, sum = 1) so that the sink needs no key; sigmoid rows just accumulate.
 //                        Calls of few tokens split the key tiles over CTAs (win_attn_combine_kernel merges).
 #include <algorithm>
@@ -21,7 +22,7 @@
 
 namespace {
 
-constexpr int WA_ROWS = 32, WA_KEYS = 32, WA_WARPS = 8, WA_QW = WA_ROWS / WA_WARPS;
+constexpr int WA_ROWS = 32, WA_KEYS = 64, WA_WARPS = 8, WA_QW = WA_ROWS / WA_WARPS;
 
 template <typename KVT>
 __global__ void __launch_bounds__(256) win_prep_kernel(WinPrepArgs a) {
@@ -71,15 +72,39 @@ __global__ void __launch_bounds__(256) win_prep_kernel(WinPrepArgs a) {
 
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
 
+// One row of a key / value tile from the cache into shared memory as floats: `n` values (dst padded with zeros up to np).
+// 16-byte global loads where the row length allows them.
+template <typename KVT>
+__device__ __forceinline__ void stage_row(const KVT* __restrict__ src, int n, int np, float* __restrict__ dst, int part, int nparts) {
+  constexpr int VEC = 16 / (int)sizeof(KVT);
+  if (src && n % VEC == 0) {
+    for (int c = part; c < n / VEC; c += nparts) {
+      float v[VEC];
+      Vec16<KVT>::load(src + c * VEC, v);
+#pragma unroll
+      for (int i = 0; i < VEC; i += 4) *reinterpret_cast<float4*>(dst + c * VEC + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    }
+    for (int i = n + part; i < np; i += nparts) dst[i] = 0.f;
+  } else {
+    for (int i = part; i < np; i += nparts) dst[i] = (src && i < n) ? to_f32(src[i]) : 0.f;
+  }
+}
+
+// value column j (< NJ) of a lane: lanes read 16-byte (8-byte, 4-byte) pieces that tile a row without bank conflicts
+template <int NJ>
+__device__ __forceinline__ int win_col(int lane, int j) {
+  return NJ == 1 ? lane : NJ == 2 ? 2 * lane + j : (j >> 2) * 128 + 4 * lane + (j & 3);
+}
+
 // NJ: value columns per lane (DV <= 32 NJ)
 template <typename KVT, int NJ>
 __global__ void __launch_bounds__(256) win_attn_kernel(WinAttnArgs a) {
   extern __shared__ __align__(16) float sm[];
   const int DKP = (a.DK + 3) & ~3, KS = DKP + 4, DVP = 32 * NJ;
   float* sQ = sm;                                  // [32][DKP]
-  float* sK = sQ + (size_t)WA_ROWS * DKP;          // [32][DKP + 4]
-  float* sV = sK + (size_t)WA_KEYS * KS;           // [32][DVP]
-  float* sP = sV + (size_t)WA_KEYS * DVP;          // [warps][QW][32]
+  float* sK = sQ + (size_t)WA_ROWS * DKP;          // [64][DKP + 4]
+  float* sV = sK + (size_t)WA_KEYS * KS;           // [64][DVP]
+  float* sP = sV + (size_t)WA_KEYS * DVP;          // [warps][QW][64]
   pdl_launch();
   pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -99,16 +124,15 @@ __global__ void __launch_bounds__(256) win_attn_kernel(WinAttnArgs a) {
   const int per = (ntiles + a.nsplit - 1) / a.nsplit;
   const int tile_lo = split * per, tile_hi = min(ntiles, tile_lo + per);
 
-  // queries
-  for (int idx = tid; idx < WA_ROWS * DKP; idx += 256) {
-    const int rr = idx / DKP, d = idx - rr * DKP;
+  // queries: 8 threads per row
+  for (int rr = tid >> 3; rr < WA_ROWS; rr += 32) {
     const int row = row0 + rr;
-    float v = 0.f;
-    if (row < nrows && d < a.DK) {
+    const float* src = nullptr;
+    if (row < nrows) {
       const int t = row / rep, h = g * rep + (row - t * rep);
-      v = a.q[(((size_t)b * a.L + t) * a.H + h) * a.DK + d];
+      src = a.q + (((size_t)b * a.L + t) * a.H + h) * a.DK;
     }
-    sQ[idx] = v;
+    stage_row<float>(src, a.DK, DKP, sQ + (size_t)rr * DKP, tid & 7, 8);
   }
   // per-row state: rows warp, warp + 8, warp + 16, warp + 24 of the tile
   float o[WA_QW][NJ], mx[WA_QW], sum[WA_QW], hv[WA_QW];
@@ -133,80 +157,87 @@ __global__ void __launch_bounds__(256) win_attn_kernel(WinAttnArgs a) {
   for (int tile = tile_lo; tile < tile_hi; ++tile) {
     __syncthreads();  // the previous tile has been used (and sQ is complete)
     const int v0 = tile * WA_KEYS;
-    for (int idx = tid; idx < WA_KEYS * DKP; idx += 256) {
-      const int kk = idx / DKP, d = idx - kk * DKP;
+    for (int kk = tid >> 3; kk < WA_KEYS; kk += 32) {  // 8 threads per key / value row
       const int vi = v0 + kk;
-      float v = 0.f;
-      if (vi < nkeys && d < a.DK) {
-        const int j = vi < ka ? vi : w_lo + (vi - ka);
-        v = to_f32(ck[(size_t)j * a.DK + d]);
-      }
-      sK[kk * KS + d] = v;
-    }
-    for (int idx = tid; idx < WA_KEYS * DVP; idx += 256) {
-      const int kk = idx / DVP, d = idx - kk * DVP;
-      const int vi = v0 + kk;
-      float v = 0.f;
-      if (vi < nkeys && d < a.DV) {
-        const int j = vi < ka ? vi : w_lo + (vi - ka);
-        v = to_f32(cv[(size_t)j * a.DV + d]);
-      }
-      sV[idx] = v;
+      const int j = vi < nkeys ? (vi < ka ? vi : w_lo + (vi - ka)) : -1;
+      stage_row<KVT>(j >= 0 ? ck + (size_t)j * a.DK : nullptr, a.DK, DKP, sK + (size_t)kk * KS, tid & 7, 8);
+      stage_row<KVT>(j >= 0 ? cv + (size_t)j * a.DV : nullptr, a.DV, DVP, sV + (size_t)kk * DVP, tid & 7, 8);
     }
     __syncthreads();
-    // scores: lane = key
-    const int vi = v0 + lane;
-    const int kj = vi < nkeys ? (vi < ka ? vi : w_lo + (vi - ka)) : -1;
-    float sc[WA_QW];
+    // scores: a lane holds keys lane and lane + 32 of the tile
+    int kj[2];
 #pragma unroll
-    for (int qi = 0; qi < WA_QW; ++qi) sc[qi] = 0.f;
-    const float4* k4 = reinterpret_cast<const float4*>(sK + (size_t)lane * KS);
+    for (int u = 0; u < 2; ++u) {
+      const int vi = v0 + lane + 32 * u;
+      kj[u] = vi < nkeys ? (vi < ka ? vi : w_lo + (vi - ka)) : -1;
+    }
+    float sc[WA_QW][2];
+#pragma unroll
+    for (int qi = 0; qi < WA_QW; ++qi) sc[qi][0] = sc[qi][1] = 0.f;
+    const float4* kA = reinterpret_cast<const float4*>(sK + (size_t)lane * KS);
+    const float4* kB = reinterpret_cast<const float4*>(sK + (size_t)(lane + 32) * KS);
+#pragma unroll 2
     for (int d4 = 0; d4 < DKP / 4; ++d4) {
-      const float4 kv = k4[d4];
+      const float4 ka4 = kA[d4], kb4 = kB[d4];
 #pragma unroll
       for (int qi = 0; qi < WA_QW; ++qi) {
         const float4 qv = reinterpret_cast<const float4*>(sQ + (size_t)(warp + qi * WA_WARPS) * DKP)[d4];
-        sc[qi] = fmaf(qv.x, kv.x, sc[qi]);
-        sc[qi] = fmaf(qv.y, kv.y, sc[qi]);
-        sc[qi] = fmaf(qv.z, kv.z, sc[qi]);
-        sc[qi] = fmaf(qv.w, kv.w, sc[qi]);
+        sc[qi][0] = fmaf(qv.x, ka4.x, sc[qi][0]); sc[qi][1] = fmaf(qv.x, kb4.x, sc[qi][1]);
+        sc[qi][0] = fmaf(qv.y, ka4.y, sc[qi][0]); sc[qi][1] = fmaf(qv.y, kb4.y, sc[qi][1]);
+        sc[qi][0] = fmaf(qv.z, ka4.z, sc[qi][0]); sc[qi][1] = fmaf(qv.z, kb4.z, sc[qi][1]);
+        sc[qi][0] = fmaf(qv.w, ka4.w, sc[qi][0]); sc[qi][1] = fmaf(qv.w, kb4.w, sc[qi][1]);
       }
     }
 #pragma unroll
     for (int qi = 0; qi < WA_QW; ++qi) {
       const int p = rpos[qi];
-      const bool vis = kj >= 0 && kj <= p && ((a.window <= 0 || p - kj < a.window) || kj < a.keep_first);
-      const float s = sc[qi] * a.scale;
-      float w;
+      bool vis[2];
+      float s2[2], w[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        vis[u] = kj[u] >= 0 && kj[u] <= p && ((a.window <= 0 || p - kj[u] < a.window) || kj[u] < a.keep_first);
+        s2[u] = sc[qi][u] * a.scale;
+      }
       if (a.kind == L3_ATTN_SIGMOID) {
-        w = vis ? sigmoid_f(s + hv[qi]) : 0.f;
+        w[0] = vis[0] ? sigmoid_f(s2[0] + hv[qi]) : 0.f;
+        w[1] = vis[1] ? sigmoid_f(s2[1] + hv[qi]) : 0.f;
       } else {
-        const float mnew = fmaxf(mx[qi], warp_max(vis ? s : -INFINITY));
+        const float mnew = fmaxf(mx[qi], warp_max(fmaxf(vis[0] ? s2[0] : -INFINITY, vis[1] ? s2[1] : -INFINITY)));
         const float alpha = mnew == -INFINITY ? 1.f : expf(mx[qi] - mnew);
-        w = vis ? expf(s - mnew) : 0.f;
-        sum[qi] = sum[qi] * alpha + warp_sum(w);
+        w[0] = vis[0] ? expf(s2[0] - mnew) : 0.f;
+        w[1] = vis[1] ? expf(s2[1] - mnew) : 0.f;
+        sum[qi] = sum[qi] * alpha + warp_sum(w[0] + w[1]);
         mx[qi] = mnew;
 #pragma unroll
         for (int j = 0; j < NJ; ++j) o[qi][j] *= alpha;
       }
-      myP[qi * WA_KEYS + lane] = w;
+      myP[qi * WA_KEYS + lane] = w[0];
+      myP[qi * WA_KEYS + lane + 32] = w[1];
     }
     __syncwarp();
-    // outputs: lane = value columns lane + 32 j
+    // outputs: a lane owns NJ value columns (win_col), read as 16-byte pieces
     for (int k0 = 0; k0 < WA_KEYS; k0 += 4) {
       float4 pw[WA_QW];
 #pragma unroll
       for (int qi = 0; qi < WA_QW; ++qi) pw[qi] = *reinterpret_cast<const float4*>(myP + qi * WA_KEYS + k0);
 #pragma unroll
-      for (int j = 0; j < NJ; ++j) {
-        const float v0f = sV[(k0 + 0) * DVP + lane + 32 * j], v1f = sV[(k0 + 1) * DVP + lane + 32 * j];
-        const float v2f = sV[(k0 + 2) * DVP + lane + 32 * j], v3f = sV[(k0 + 3) * DVP + lane + 32 * j];
+      for (int kk = 0; kk < 4; ++kk) {
+        float vv[NJ];
+        const float* vr = sV + (size_t)(k0 + kk) * DVP;
+        if (NJ == 1) vv[0] = vr[lane];
+        else if (NJ == 2) { const float2 t2 = *reinterpret_cast<const float2*>(vr + 2 * lane); vv[0] = t2.x; vv[1] = t2.y; }
+        else {
+#pragma unroll
+          for (int c = 0; c < NJ / 4; ++c) {
+            const float4 t4 = *reinterpret_cast<const float4*>(vr + c * 128 + 4 * lane);
+            vv[4 * c] = t4.x; vv[4 * c + 1] = t4.y; vv[4 * c + 2] = t4.z; vv[4 * c + 3] = t4.w;
+          }
+        }
 #pragma unroll
         for (int qi = 0; qi < WA_QW; ++qi) {
-          o[qi][j] = fmaf(pw[qi].x, v0f, o[qi][j]);
-          o[qi][j] = fmaf(pw[qi].y, v1f, o[qi][j]);
-          o[qi][j] = fmaf(pw[qi].z, v2f, o[qi][j]);
-          o[qi][j] = fmaf(pw[qi].w, v3f, o[qi][j]);
+          const float pk = kk == 0 ? pw[qi].x : kk == 1 ? pw[qi].y : kk == 2 ? pw[qi].z : pw[qi].w;
+#pragma unroll
+          for (int j = 0; j < NJ; ++j) o[qi][j] = fmaf(pk, vv[j], o[qi][j]);
         }
       }
     }
@@ -221,15 +252,17 @@ __global__ void __launch_bounds__(256) win_attn_kernel(WinAttnArgs a) {
     if (a.nsplit > 1) {  // partial (o, max, sum) of this split
       const size_t pi = (r * a.H + h) * a.nsplit + split;
 #pragma unroll
-      for (int j = 0; j < NJ; ++j)
-        if (lane + 32 * j < a.DV) a.part_o[pi * a.DV + lane + 32 * j] = o[qi][j];
+      for (int j = 0; j < NJ; ++j) {
+        const int d = win_col<NJ>(lane, j);
+        if (d < a.DV) a.part_o[pi * a.DV + d] = o[qi][j];
+      }
       if (lane == 0) { a.part_ml[pi * 2] = mx[qi]; a.part_ml[pi * 2 + 1] = sum[qi]; }
       continue;
     }
     const float mul = a.out_scale * (a.kind == L3_ATTN_SIGMOID ? 1.f : (sum[qi] > 0.f ? 1.0f / sum[qi] : 0.f));
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
-      const int d = lane + 32 * j;
+      const int d = win_col<NJ>(lane, j);
       if (d < a.DV) {
         const float v = o[qi][j] * mul;
         const size_t oi = r * a.ld_out + (size_t)h * a.DV + d;
@@ -240,38 +273,36 @@ __global__ void __launch_bounds__(256) win_attn_kernel(WinAttnArgs a) {
   }
 }
 
-// a warp per (row, head): merges the splits' partials
+// a thread per (row, head, value column): merges the splits' partials
 __global__ void __launch_bounds__(128) win_attn_combine_kernel(WinAttnArgs a) {
   pdl_launch();
   pdl_wait();
-  const int lane = threadIdx.x & 31;
-  const size_t rh = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (rh >= (size_t)a.B * a.L * a.H) return;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)a.B * a.L * a.H * a.DV) return;
+  const size_t rh = (size_t)(i / a.DV);
+  const int d = (int)(i - (int64_t)rh * a.DV);
   const size_t r = rh / a.H;
   const int h = (int)(rh - r * a.H);
   float M = -INFINITY;
   if (a.kind != L3_ATTN_SIGMOID)
     for (int s = 0; s < a.nsplit; ++s) M = fmaxf(M, a.part_ml[(rh * a.nsplit + s) * 2]);
-  float den = 0.f;
-  for (int d = lane; d < a.DV; d += 32) {
-    float acc = 0.f;
-    den = 0.f;
-    for (int s = 0; s < a.nsplit; ++s) {
-      const size_t pi = rh * a.nsplit + s;
-      float f = 1.f;
-      if (a.kind != L3_ATTN_SIGMOID) {
-        const float ms = a.part_ml[pi * 2];
-        f = ms == -INFINITY ? 0.f : expf(ms - M);
-        den = fmaf(a.part_ml[pi * 2 + 1], f, den);
-      }
-      acc = fmaf(a.part_o[pi * a.DV + d], f, acc);
+  float acc = 0.f, den = 0.f;
+#pragma unroll 4
+  for (int s = 0; s < a.nsplit; ++s) {
+    const size_t pi = rh * a.nsplit + s;
+    float f = 1.f;
+    if (a.kind != L3_ATTN_SIGMOID) {
+      const float ms = a.part_ml[pi * 2];
+      f = ms == -INFINITY ? 0.f : expf(ms - M);
+      den = fmaf(a.part_ml[pi * 2 + 1], f, den);
     }
-    const float mul = a.out_scale * (a.kind == L3_ATTN_SIGMOID ? 1.f : (den > 0.f ? 1.0f / den : 0.f));
-    const float v = acc * mul;
-    const size_t oi = r * a.ld_out + (size_t)h * a.DV + d;
-    a.out[oi] = v;
-    if (a.out16) a.out16[oi] = __float2bfloat16_rn(v);
+    acc = fmaf(a.part_o[pi * a.DV + d], f, acc);
   }
+  const float mul = a.out_scale * (a.kind == L3_ATTN_SIGMOID ? 1.f : (den > 0.f ? 1.0f / den : 0.f));
+  const float v = acc * mul;
+  const size_t oi = r * a.ld_out + (size_t)h * a.DV + d;
+  a.out[oi] = v;
+  if (a.out16) a.out16[oi] = __float2bfloat16_rn(v);
 }
 
 size_t win_attn_smem(int DK, int NJ) {
@@ -314,8 +345,8 @@ int win_attn_splits(int B, int L, int H, int G, int window, int keep_first, int 
   int keys = max_keys;
   if (window > 0) keys = std::min(keys, window + L + keep_first);
   const int tiles = (keys + WA_KEYS - 1) / WA_KEYS;
-  // at least two key tiles per split, aimed at two CTAs per SM
-  return std::max(1, std::min(std::min(max_split, tiles / 2), (2 * 148) / std::max(1, ctas)));
+  // a key tile or more per split, aimed at two CTAs per SM
+  return std::max(1, std::min(std::min(max_split, tiles), (2 * 148) / std::max(1, ctas)));
 }
 
 size_t win_attn_part_floats(int max_rows, int H, int DV, int max_split) { return (size_t)max_rows * H * max_split * DV; }
@@ -335,6 +366,6 @@ cudaError_t launch_win_attn(const WinAttnArgs& a, bool kv_bf16, cudaStream_t s) 
   const dim3 grid((a.L * rep + WA_ROWS - 1) / WA_ROWS, a.G, a.B * a.nsplit);
   cudaError_t e = kv_bf16 ? launch_win_t<bf16>(a, grid, s) : launch_win_t<float>(a, grid, s);
   if (e != cudaSuccess || a.nsplit == 1) return e;
-  const int64_t rh = (int64_t)a.B * a.L * a.H;
-  return launch_k(win_attn_combine_kernel, dim3((unsigned)((rh + 3) / 4)), dim3(128), 0, s, a);
+  const int64_t n = (int64_t)a.B * a.L * a.H * a.DV;
+  return launch_k(win_attn_combine_kernel, dim3((unsigned)((n + 127) / 128)), dim3(128), 0, s, a);
 }
