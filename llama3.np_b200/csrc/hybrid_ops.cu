@@ -30,16 +30,18 @@ __global__ void __launch_bounds__(256) ssd_prep_kernel(SsdPrepArgs a) {
   for (int h = threadIdx.x; h < a.H; h += blockDim.x) {
     const float dt = softplus_f(row[a.dt_off + h] + a.dt_bias[h]);
     sdt[h] = dt;
-    a.decay_out[(size_t)r * a.H + h] = expf(-expf(a.A_log[h]) * dt);
+    if (blockIdx.y == 0) a.decay_out[(size_t)r * a.H + h] = expf(-expf(a.A_log[h]) * dt);
   }
   __syncthreads();
-  const float* tail = a.conv_tail + (size_t)b * C * T1;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  float* tail = a.conv_tail + (size_t)b * C * T1;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
     float acc = a.conv_b ? a.conv_b[c] : 0.f;
     for (int j = 0; j < a.taps; ++j) {
       const int tt = t - T1 + j;  // time inside this call; negative: from the tail
       const float xin = tt >= 0 ? a.proj[(size_t)(b * a.L + tt) * a.ld + a.xbc_off + c] : tail[(size_t)c * T1 + (T1 + tt)];
       acc = fmaf(a.conv_w[(size_t)c * a.taps + j], xin, acc);
+      // a call of one token moves the tail on here: this thread alone reads and writes channel c's entries
+      if (a.update_tail && j >= 1 && j <= T1) tail[(size_t)c * T1 + (j - 1)] = xin;
     }
     const float s = silu_ref(acc);
     if (c < inner) {
@@ -67,34 +69,45 @@ __global__ void gla_prep_kernel(const float* __restrict__ q, int ld, float q_mul
   g_out[i] = expf(-softplus_f(-zz) * inv_tau);  // log sigmoid(z) = -softplus(-z)
 }
 
-__global__ void __launch_bounds__(256) mix_out_kernel(MixOutArgs a) {
+// wpg warps share a group (wpg in 1, 2, 4, 8); a CTA of 8 warps holds 8 / wpg groups, blockIdx.y walks the groups
+__global__ void __launch_bounds__(256) mix_out_kernel(MixOutArgs a, int wpg) {
+  __shared__ float red[8];
   pdl_launch();
   pdl_wait();
   const size_t r = blockIdx.x;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gpc = 8 / wpg, g = blockIdx.y * gpc + warp / wpg, sub = warp % wpg;
+  const bool live = g * a.group < a.n;
   const float* orow = a.o + r * a.n;
   const float* grow = a.gate ? a.gate + r * a.ld_gate : nullptr;
   const float* xrow = a.skip_d ? a.skip_x + r * a.n : nullptr;
-  auto act = [&](float g) { return a.gate_act ? g * sigmoid_f(g) : sigmoid_f(g); };
+  auto act = [&](float z) { return a.gate_act ? z * sigmoid_f(z) : sigmoid_f(z); };
   auto val = [&](int i) {
     float y = orow[i];
     if (xrow) y = fmaf(a.skip_d[i / a.DV], xrow[i], y);
     if (grow && a.pre_gate) y *= act(grow[i]);
     return y;
   };
-  for (int g = warp; g * a.group < a.n; g += nw) {  // a warp per group
-    const int base = g * a.group;
-    float ss = 0.f;
-    for (int i = lane; i < a.group; i += 32) { const float y = val(base + i); ss = fmaf(y, y, ss); }
-    const float rinv = 1.0f / sqrtf(warp_sum(ss) / (float)a.group + a.eps);
-    for (int i = lane; i < a.group; i += 32) {
-      const int c = base + i;
-      float v = val(c) * rinv * a.w[c % a.wlen];
-      if (grow && !a.pre_gate) v *= act(grow[c]);
-      v *= a.out_scale;
-      a.out[r * a.ld_out + c] = v;
-      if (a.out16) a.out16[r * a.ld_out + c] = __float2bfloat16_rn(v);
-    }
+  const int base = g * a.group;
+  float ss = 0.f;
+  if (live)
+    for (int i = sub * 32 + lane; i < a.group; i += wpg * 32) { const float y = val(base + i); ss = fmaf(y, y, ss); }
+  ss = warp_sum(ss);
+  if (wpg > 1) {
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    ss = 0.f;
+    for (int w = 0; w < wpg; ++w) ss += red[(warp / wpg) * wpg + w];
+  }
+  if (!live) return;
+  const float rinv = 1.0f / sqrtf(ss / (float)a.group + a.eps);
+  for (int i = sub * 32 + lane; i < a.group; i += wpg * 32) {
+    const int c = base + i;
+    float v = val(c) * rinv * a.w[c % a.wlen];
+    if (grow && !a.pre_gate) v *= act(grow[c]);
+    v *= a.out_scale;
+    a.out[r * a.ld_out + c] = v;
+    if (a.out16) a.out16[r * a.ld_out + c] = __float2bfloat16_rn(v);
   }
 }
 
@@ -121,7 +134,10 @@ __global__ void concat_rows_kernel(const float* __restrict__ a, const float* __r
 }  // namespace
 
 cudaError_t launch_ssd_prep(const SsdPrepArgs& a, int rows, cudaStream_t s) {
-  return launch_k(ssd_prep_kernel, dim3(rows), dim3(256), (size_t)a.H * sizeof(float), s, a);
+  if (a.update_tail && a.L != 1) return cudaErrorInvalidValue;
+  const int C = a.H * a.DV + 2 * a.G * a.N;
+  const int parts = rows <= 8 ? std::max(1, std::min(32, C / 256)) : 1;  // few rows: a row's channels spread over CTAs
+  return launch_k(ssd_prep_kernel, dim3(rows, parts), dim3(256), (size_t)a.H * sizeof(float), s, a);
 }
 
 cudaError_t launch_gla_prep(const float* q, int ld, float q_mul, const float* z, int ld_z, const float* bias, float tau, int rows,
@@ -134,8 +150,9 @@ cudaError_t launch_gla_prep(const float* q, int ld, float q_mul, const float* z,
 cudaError_t launch_mix_out(const MixOutArgs& a, int rows, cudaStream_t s) {
   if (a.group < 1 || a.n % a.group != 0) return cudaErrorInvalidValue;
   const int groups = a.n / a.group;
-  const int threads = std::min(256, 32 * std::max(1, groups));
-  return launch_k(mix_out_kernel, dim3(rows), dim3(threads), 0, s, a);
+  const int wpg = a.group >= 1024 ? 8 : a.group >= 512 ? 4 : a.group >= 256 ? 2 : 1;  // warps per group
+  const int gpc = 8 / wpg;
+  return launch_k(mix_out_kernel, dim3(rows, (groups + gpc - 1) / gpc), dim3(256), 0, s, a, wpg);
 }
 
 cudaError_t launch_softcap(float* x, int64_t n, float cap, cudaStream_t s) {

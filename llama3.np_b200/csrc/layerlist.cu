@@ -1245,9 +1245,9 @@ static int ll_mix_unit(L3Model* m, LLLayer& Ly, LLState& St, const float* pin, i
     pa.proj = pin; pa.ld = ld; pa.xbc_off = Ly.off_q; pa.dt_off = Ly.off_b; pa.conv_w = Ly.conv_w; pa.conv_b = Ly.conv_b;
     pa.conv_tail = St.conv_tail; pa.A_log = Ly.A_log; pa.dt_bias = Ly.dt_bias;
     pa.x_out = ll->xs; pa.v_out = ll->rv; pa.k_out = ll->rk; pa.q_out = m->q; pa.decay_out = ll->rg;
-    pa.L = L; pa.H = H; pa.G = G; pa.N = DK; pa.DV = DV; pa.taps = s.conv_taps;
+    pa.L = L; pa.H = H; pa.G = G; pa.N = DK; pa.DV = DV; pa.taps = s.conv_taps; pa.update_tail = L == 1;
     LAUNCH(m, launch_ssd_prep(pa, ntok, m->stream));
-    if (s.conv_taps > 1) LAUNCH(m, launch_conv_tail(St.conv_tail, pin + Ly.off_q, ld, B, L, O + 2 * gn, s.conv_taps - 1, m->stream));
+    if (s.conv_taps > 1 && L > 1) LAUNCH(m, launch_conv_tail(St.conv_tail, pin + Ly.off_q, ld, B, L, O + 2 * gn, s.conv_taps - 1, m->stream));
     ra.mode = 2; ra.q = m->q; ra.k = ll->rk; ra.v = ll->rv; ra.ld_q = ra.ld_k = gn; ra.ld_v = O; ra.g = ll->rg; ra.g_head = 1; ra.rep = H / G;
     LAUNCH(m, launch_recur(ra, m->stream));
     mo.skip_d = Ly.skip_d; mo.skip_x = ll->xs; mo.gate = pin + Ly.off_g; mo.ld_gate = ld; mo.gate_act = 1; mo.pre_gate = 1;
@@ -1270,9 +1270,9 @@ static int ll_mix_unit(L3Model* m, LLLayer& Ly, LLState& St, const float* pin, i
     pa.proj = pin; pa.ld = ld; pa.beta_off = Ly.off_b; pa.dt_in = dt; pa.ld_dt = nd;
     pa.conv_w = Ly.conv_w; pa.conv_tail = St.conv_tail; pa.A_log = Ly.A_log; pa.dt_bias = Ly.dt_bias;
     pa.q_out = m->q; pa.k_out = ll->rk; pa.v_out = ll->rv; pa.decay_out = ll->rg; pa.beta_out = ll->rbeta;
-    pa.L = L; pa.H = H; pa.G = G; pa.DK = DK; pa.DV = DV; pa.taps = s.conv_taps;
+    pa.L = L; pa.H = H; pa.G = G; pa.DK = DK; pa.DV = DV; pa.taps = s.conv_taps; pa.update_tail = L == 1;
     LAUNCH(m, launch_delta_prep(pa, ntok, m->stream));
-    if (s.conv_taps > 1) LAUNCH(m, launch_conv_tail(St.conv_tail, pin, ld, B, L, 2 * nq + O, s.conv_taps - 1, m->stream));
+    if (s.conv_taps > 1 && L > 1) LAUNCH(m, launch_conv_tail(St.conv_tail, pin, ld, B, L, 2 * nq + O, s.conv_taps - 1, m->stream));
     ra.mode = 1; ra.q = m->q; ra.k = ll->rk; ra.v = ll->rv; ra.ld_q = ra.ld_k = nq; ra.ld_v = O;
     ra.g = ll->rg; ra.beta = ll->rbeta; ra.rep = H / G;
     LAUNCH(m, launch_recur(ra, m->stream));

@@ -35,7 +35,7 @@ struct DeltaPrepArgs {
   const float* dt_in;     // [rows, ld_dt]: decay logits per (head, key channel) before the bias
   int ld_dt;
   const float* conv_w;    // [C, taps], last tap = current token
-  const float* conv_tail; // [maxB, C, taps - 1]
+  float* conv_tail;       // [maxB, C, taps - 1]
   const float* A_log;     // [H]
   const float* dt_bias;   // [H * DK]
   float *q_out, *k_out;   // [rows, G * DK]
@@ -43,6 +43,7 @@ struct DeltaPrepArgs {
   float* decay_out;       // [rows, H * DK]
   float* beta_out;        // [rows, H]
   int L, H, G, DK, DV, taps;
+  int update_tail;        // L == 1 only: the kernel also moves conv_tail on by this token (no launch_conv_tail afterwards)
 };
 cudaError_t launch_delta_prep(const DeltaPrepArgs& a, int rows, cudaStream_t s);
 cudaError_t launch_conv_tail(float* tail, const float* proj, int ld, int B, int L, int C, int T1, cudaStream_t s);
@@ -282,7 +283,7 @@ struct SsdPrepArgs {
   int ld, xbc_off, dt_off;
   const float* conv_w;    // [C, taps], last tap = current token
   const float* conv_b;    // [C]
-  const float* conv_tail; // [maxB, C, taps - 1]
+  float* conv_tail;       // [maxB, C, taps - 1]
   const float* A_log;     // [H]
   const float* dt_bias;   // [H]
   float* x_out;           // [rows, H * DV] convolved x (the skip term reads it)
@@ -290,6 +291,7 @@ struct SsdPrepArgs {
   float *k_out, *q_out;   // [rows, G * N] B and C
   float* decay_out;       // [rows, H] exp(-exp(A_log) dt)
   int L, H, G, N, DV, taps;
+  int update_tail;        // L == 1 only: the kernel also moves conv_tail on by this token (no launch_conv_tail afterwards)
 };
 cudaError_t launch_ssd_prep(const SsdPrepArgs& a, int rows, cudaStream_t s);
 // q_out[r, i] = q[r * ld + i] * q_mul;  g_out[r, i] = sigmoid(z[r * ld_z + i] + bias[i])^(1 / tau)   (i < n)

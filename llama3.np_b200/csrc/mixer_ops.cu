@@ -8,7 +8,8 @@
 //                            (the values of this attention) to the KV cache
 //  * side_mul_kernel         act(g) * E[token, layer slice]    (per-layer token input)
 //  * delta_prep_kernel       short causal convolutions + silu, unit-length q / k, decay and write strength of
-//                            the gated delta rule; conv_tail_kernel moves the convolutions' tails on
+//                            the gated delta rule; conv_tail_kernel moves the convolutions' tails on (a call of one
+//                            token lets delta_prep_kernel do that itself)
 //  * rmsnorm_rows_kernel     plain RMS norm of chosen rows, any width (ahead of the LM head)
 //  * to_bf16_kernel          bf16 mirror of fp32 rows
 #include <algorithm>
@@ -132,46 +133,55 @@ __global__ void side_mul_kernel(float* __restrict__ g, int n, int rows, const WT
   if (out16) out16[i] = __float2bfloat16_rn(v);
 }
 
-// One CTA per token row.  Input of channel c at time t' < 0 of the call comes from the tail [C][taps-1]
-// (oldest first) that earlier calls left.
+// Input of channel c at time t' < 0 of the call comes from the tail [C][taps-1] (oldest first) that earlier calls left.
+// The work of a token row is a list of items - a q or k head (convolution + silu + unit length), a v head (convolution +
+// silu), a head's decays, the write strengths - and every warp of the row's CTAs (blockIdx.y of them: few rows spread a
+// row over several CTAs) takes items round-robin; no item needs another warp.
 __global__ void __launch_bounds__(256) delta_prep_kernel(DeltaPrepArgs a) {
-  extern __shared__ float sm[];  // [nq + nk] convolved q | k of this row
+  extern __shared__ float sm[];  // [warps][DK] the convolved head a warp works on
   pdl_launch();
   pdl_wait();
   const int r = blockIdx.x;
   const int b = r / a.L, t = r - b * a.L;
   const int nq = a.G * a.DK, nv = a.H * a.DV, C = 2 * nq + nv, T1 = a.taps - 1;
-  const float* tail = a.conv_tail + (size_t)b * C * T1;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  float* tail = a.conv_tail + (size_t)b * C * T1;
+  float* buf = sm + (size_t)warp * a.DK;
+  auto conv = [&](int c) {
     float acc = 0.f;
     for (int j = 0; j < a.taps; ++j) {
       const int tt = t - T1 + j;  // time inside this call; negative: from the tail
       const float xin = tt >= 0 ? a.proj[(size_t)(b * a.L + tt) * a.ld + c] : tail[(size_t)c * T1 + (T1 + tt)];
       acc = fmaf(a.conv_w[(size_t)c * a.taps + j], xin, acc);
+      // a call of one token moves the tail on here: this thread alone reads and writes channel c's entries
+      if (a.update_tail && j >= 1 && j <= T1) tail[(size_t)c * T1 + (j - 1)] = xin;
     }
-    const float s = silu_ref(acc);
-    if (c < 2 * nq) sm[c] = s;
-    else a.v_out[(size_t)r * nv + (c - 2 * nq)] = s;
+    return silu_ref(acc);
+  };
+  const int n_items = 2 * a.G + 2 * a.H + 1;
+  for (int item = blockIdx.y * nw + warp; item < n_items; item += gridDim.y * nw) {
+    if (item < 2 * a.G) {  // a q or k head: unit length; q also times DK^-1/2
+      float ss = 0.f;
+      for (int i = lane; i < a.DK; i += 32) { const float v = conv(item * a.DK + i); buf[i] = v; ss = fmaf(v, v, ss); }
+      float rinv = 1.0f / sqrtf(warp_sum(ss) + 1e-6f);
+      const bool is_q = item < a.G;
+      if (is_q) rinv *= 1.0f / sqrtf((float)a.DK);
+      float* dst = is_q ? a.q_out + (size_t)r * nq + (size_t)item * a.DK : a.k_out + (size_t)r * nq + (size_t)(item - a.G) * a.DK;
+      for (int i = lane; i < a.DK; i += 32) dst[i] = buf[i] * rinv;  // a lane reads back what it wrote itself
+    } else if (item < 2 * a.G + a.H) {
+      const int h = item - 2 * a.G;
+      for (int i = lane; i < a.DV; i += 32) a.v_out[(size_t)r * nv + (size_t)h * a.DV + i] = conv(2 * nq + h * a.DV + i);
+    } else if (item < 2 * a.G + 2 * a.H) {  // decay per key channel of a head
+      const int h = item - 2 * a.G - a.H;
+      const float rate = expf(a.A_log[h]);
+      for (int i = lane; i < a.DK; i += 32) {
+        const int c = h * a.DK + i;
+        a.decay_out[(size_t)r * a.H * a.DK + c] = expf(-rate * softplus_f(a.dt_in[(size_t)r * a.ld_dt + c] + a.dt_bias[c]));
+      }
+    } else {
+      for (int h = lane; h < a.H; h += 32) a.beta_out[(size_t)r * a.H + h] = sigmoid_f(a.proj[(size_t)r * a.ld + a.beta_off + h]);
+    }
   }
-  __syncthreads();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  for (int g = warp; g < 2 * a.G; g += nw) {  // unit length per head; q also times DK^-1/2
-    const float* src = sm + (size_t)g * a.DK;
-    float ss = 0.f;
-    for (int i = lane; i < a.DK; i += 32) ss = fmaf(src[i], src[i], ss);
-    float rinv = 1.0f / sqrtf(warp_sum(ss) + 1e-6f);
-    const bool is_q = g < a.G;
-    if (is_q) rinv *= 1.0f / sqrtf((float)a.DK);
-    float* dst = is_q ? a.q_out + (size_t)r * nq + (size_t)g * a.DK : a.k_out + (size_t)r * nq + (size_t)(g - a.G) * a.DK;
-    for (int i = lane; i < a.DK; i += 32) dst[i] = src[i] * rinv;
-  }
-  const int nd = a.H * a.DK;
-  for (int i = threadIdx.x; i < nd; i += blockDim.x) {  // decay per head and key channel
-    const float rate = expf(a.A_log[i / a.DK]);
-    a.decay_out[(size_t)r * nd + i] = expf(-rate * softplus_f(a.dt_in[(size_t)r * a.ld_dt + i] + a.dt_bias[i]));
-  }
-  for (int h = threadIdx.x; h < a.H; h += blockDim.x)
-    a.beta_out[(size_t)r * a.H + h] = sigmoid_f(a.proj[(size_t)r * a.ld + a.beta_off + h]);
 }
 
 // new tail[r] = element L + r of (old tail | the call's L inputs); ascending r never reads what it wrote
@@ -258,12 +268,15 @@ cudaError_t launch_side_mul(float* g, int n, int rows, const void* table, bool t
 }
 
 cudaError_t launch_delta_prep(const DeltaPrepArgs& a, int rows, cudaStream_t s) {
-  const size_t smem = (size_t)2 * a.G * a.DK * sizeof(float);
+  if (a.update_tail && a.L != 1) return cudaErrorInvalidValue;
+  const size_t smem = (size_t)8 * a.DK * sizeof(float);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(delta_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  return launch_k(delta_prep_kernel, dim3(rows), dim3(256), smem, s, a);
+  const int items = 2 * a.G + 2 * a.H + 1;
+  const int parts = rows <= 8 ? std::max(1, std::min(32, (items + 7) / 8)) : 1;  // few rows: a row's items spread over CTAs
+  return launch_k(delta_prep_kernel, dim3(rows, parts), dim3(256), smem, s, a);
 }
 
 cudaError_t launch_conv_tail(float* tail, const float* proj, int ld, int B, int L, int C, int T1, cudaStream_t s) {
