@@ -26,7 +26,7 @@ constexpr int WA_ROWS = 32, WA_KEYS = 64, WA_WARPS = 8, WA_QW = WA_ROWS / WA_WAR
 
 template <typename KVT>
 __global__ void __launch_bounds__(256) win_prep_kernel(WinPrepArgs a) {
-  extern __shared__ float sm[];  // [warps][DK]
+  extern __shared__ float sm[];  // [warps][DK] | cosines and sines of the row's angles [rot_dims / 2] each
   pdl_launch();
   pdl_wait();
   const int r = blockIdx.x;
@@ -36,16 +36,18 @@ __global__ void __launch_bounds__(256) win_prep_kernel(WinPrepArgs a) {
   const float* row = a.proj + (size_t)r * a.ld;
   float* buf = sm + (size_t)warp * a.DK;
   const int half = a.rot_dims / 2;
+  float* cs = sm + (size_t)nw * a.DK;
+  float* sn = cs + half;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * a.inv_freq[i], &sn[i], &cs[i]);  // once per row, every head reads them
+  __syncthreads();
   for (int v = warp; v < a.H + a.G; v += nw) {
     const bool is_q = v < a.H;
     const float* src = row + (is_q ? a.q_off + (size_t)v * a.DK : a.k_off + (size_t)(v - a.H) * a.DK);
     for (int i = lane; i < half; i += 32) {
       const int i0 = a.rot_layout ? i : 2 * i, i1 = a.rot_layout ? i + half : 2 * i + 1;
-      float sn, cs;
-      sincosf((float)pos * a.inv_freq[i], &sn, &cs);
       const float u = src[i0], w = src[i1];
-      buf[i0] = u * cs - w * sn;
-      buf[i1] = w * cs + u * sn;
+      buf[i0] = u * cs[i] - w * sn[i];
+      buf[i1] = w * cs[i] + u * sn[i];
     }
     for (int i = a.rot_dims + lane; i < a.DK; i += 32) buf[i] = src[i];
     __syncwarp();
@@ -310,7 +312,7 @@ size_t win_attn_smem(int DK, int NJ) {
   return ((size_t)WA_ROWS * DKP + (size_t)WA_KEYS * (DKP + 4) + (size_t)WA_KEYS * 32 * NJ + (size_t)WA_WARPS * WA_QW * WA_KEYS) * sizeof(float);
 }
 
-int win_nj(int DV) { return DV <= 32 ? 1 : DV <= 64 ? 2 : DV <= 128 ? 4 : 8; }
+int win_nj(int DV) { return DV <= 32 ? 1 : DV <= 64 ? 2 : DV <= 128 ? 4 : DV <= 256 ? 8 : 16; }
 
 template <typename KVT, int NJ>
 cudaError_t launch_win_nj(const WinAttnArgs& a, dim3 grid, cudaStream_t s) {
@@ -328,14 +330,15 @@ cudaError_t launch_win_t(const WinAttnArgs& a, dim3 grid, cudaStream_t s) {
     case 1: return launch_win_nj<KVT, 1>(a, grid, s);
     case 2: return launch_win_nj<KVT, 2>(a, grid, s);
     case 4: return launch_win_nj<KVT, 4>(a, grid, s);
-    default: return launch_win_nj<KVT, 8>(a, grid, s);
+    case 8: return launch_win_nj<KVT, 8>(a, grid, s);
+    default: return launch_win_nj<KVT, 16>(a, grid, s);
   }
 }
 
 }  // namespace
 
 bool win_attn_supported(int DK, int DV) {
-  return DK >= 1 && DV >= 1 && DV <= 256 && win_attn_smem(DK, win_nj(DV)) <= 200 * 1024;
+  return DK >= 1 && DV >= 1 && DV <= 512 && win_attn_smem(DK, win_nj(DV)) <= 220 * 1024;
 }
 
 int win_attn_splits(int B, int L, int H, int G, int window, int keep_first, int max_keys, int max_split) {
@@ -354,7 +357,7 @@ size_t win_attn_part_floats(int max_rows, int H, int DV, int max_split) { return
 cudaError_t launch_win_prep(const WinPrepArgs& a, int rows, bool kv_bf16, cudaStream_t s) {
   const int vecs = a.H + a.G;
   const int threads = std::min(256, 32 * std::max(1, std::min(vecs, 8)));
-  const size_t smem = (size_t)(threads / 32) * a.DK * sizeof(float);
+  const size_t smem = ((size_t)(threads / 32) * a.DK + a.rot_dims) * sizeof(float);
   if (kv_bf16) return launch_k(win_prep_kernel<bf16>, dim3(rows), dim3(threads), smem, s, a);
   return launch_k(win_prep_kernel<float>, dim3(rows), dim3(threads), smem, s, a);
 }

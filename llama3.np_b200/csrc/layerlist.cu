@@ -199,7 +199,7 @@ extern "C" int l3_create_stack(const L3StackConfig* c, const L3LayerSpec* specs,
   REQUIRE(nullptr, !c->parallel || (c->norm_input && !c->token_shift && !c->norm_scalar && c->loop_times == 0), "parallel layers are pre-norm layers without token shift, single-weight norms or loops");
   REQUIRE(nullptr, c->parallel || (!c->norm_center && !c->layer_scale && !c->canon_taps && !c->depth_avg), "centred norms, layer scales, input convolutions and the depth average are built for parallel layers");
   REQUIRE(nullptr, c->canon_taps >= 0 && c->canon_taps <= 64, "bad canon_taps");
-  REQUIRE(nullptr, c->norm_groups >= 0 && c->norm_groups <= 32 && (c->norm_groups <= 1 || c->width % c->norm_groups == 0), "bad norm_groups");
+  REQUIRE(nullptr, c->norm_groups >= 0 && c->norm_groups <= 128 && (c->norm_groups <= 1 || c->width % c->norm_groups == 0), "bad norm_groups");
   REQUIRE(nullptr, (c->norm_input && !c->parallel) || (c->norm_groups <= 1 && !c->embed_norm && !c->loop_in && !(c->logit_softcap > 0.f)),
           "grouped norms, the embedding norm, the loop's entry projection and the logit cap are built for pre-norm stacks");
   REQUIRE(nullptr, !c->loop_in || c->loop_times > 0, "loop_in without a loop");

@@ -204,17 +204,28 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restri
                                                            int D, int src_mul, int src_add, const int32_t* __restrict__ src_rows,
                                                            int groups, float* __restrict__ out, bf16* __restrict__ out16) {
   __shared__ float red[32];
-  __shared__ float rg[32];
+  __shared__ float rg[128];
   pdl_launch();
   pdl_wait();
   const size_t r = blockIdx.x;
   const float* xr = x + (src_rows ? (size_t)src_rows[r] : r * src_mul + src_add) * D;
   const int gs = D / groups;
-  for (int g = 0; g < groups; ++g) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  const int wpg = max(1, nw / groups), gpr = nw / wpg;  // warps per group, groups settled per round
+  for (int g0 = 0; g0 < groups; g0 += gpr) {
+    const int g = g0 + warp / wpg, sub = warp % wpg;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < gs; i += blockDim.x) { const float v = xr[g * gs + i]; ss = fmaf(v, v, ss); }
-    const float tot = block_sum(ss, red);
-    if (threadIdx.x == 0) rg[g] = 1.0f / sqrtf(tot / (float)gs + eps);
+    if (g < groups && warp < gpr * wpg)
+      for (int i = sub * 32 + lane; i < gs; i += wpg * 32) { const float v = xr[g * gs + i]; ss = fmaf(v, v, ss); }
+    ss = warp_sum(ss);
+    __syncthreads();
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    if (g < groups && warp < gpr * wpg && sub == 0 && lane == 0) {
+      float tot = 0.f;
+      for (int w = 0; w < wpg; ++w) tot += red[warp + w];
+      rg[g] = 1.0f / sqrtf(tot / (float)gs + eps);
+    }
   }
   __syncthreads();
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
@@ -286,7 +297,7 @@ cudaError_t launch_conv_tail(float* tail, const float* proj, int ld, int B, int 
 
 cudaError_t launch_rmsnorm_rows(const float* x, const float* w, float eps, int rows, int D, int src_mul, int src_add,
                                 const int32_t* src_rows, float* out, bf16* out16, cudaStream_t s, int groups) {
-  if (groups < 1 || groups > 32 || D % groups != 0) return cudaErrorInvalidValue;
+  if (groups < 1 || groups > 128 || D % groups != 0) return cudaErrorInvalidValue;
   return launch_k(rmsnorm_rows_kernel, dim3(rows), dim3(row_threads(D)), 0, s, x, w, eps, D, src_mul, src_add, src_rows, groups, out, out16);
 }
 

@@ -25,19 +25,32 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return t;
 }
 
-// 1 / rms of every one of `groups` equal consecutive parts of a row, into out[groups] (shared memory)
+// 1 / rms of every one of `groups` equal consecutive parts of a row, into out[groups] (shared memory).  The CTA's warps
+// share the groups: with fewer groups than warps several warps sum one group, and a round of the loop settles as many
+// groups as fit (one round for up to 8 groups of a 256-thread CTA).
 __device__ __forceinline__ void row_rinv(const float* __restrict__ row, int D, int groups, float eps, float* red, float* out) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
   const int gs = D / groups;
-  for (int g = 0; g < groups; ++g) {
+  const int wpg = max(1, nw / groups), gpr = nw / wpg;  // warps per group, groups per round
+  for (int g0 = 0; g0 < groups; g0 += gpr) {
+    const int g = g0 + warp / wpg, sub = warp % wpg;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < gs; i += blockDim.x) { const float v = row[g * gs + i]; ss = fmaf(v, v, ss); }
-    const float tot = block_sum(ss, red);
-    if (threadIdx.x == 0) out[g] = 1.0f / sqrtf(tot / (float)gs + eps);
+    if (g < groups && warp < gpr * wpg)
+      for (int i = sub * 32 + lane; i < gs; i += wpg * 32) { const float v = row[g * gs + i]; ss = fmaf(v, v, ss); }
+    ss = warp_sum(ss);
+    __syncthreads();  // red may still be read from the previous round
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    if (g < groups && warp < gpr * wpg && sub == 0 && lane == 0) {
+      float tot = 0.f;
+      for (int w = 0; w < wpg; ++w) tot += red[warp + w];
+      out[g] = 1.0f / sqrtf(tot / (float)gs + eps);
+    }
   }
   __syncthreads();
 }
 
-constexpr int NORM_GROUPS_MAX = 32;
+constexpr int NORM_GROUPS_MAX = 128;
 
 __global__ void __launch_bounds__(256) prenorm_shift_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps,
                                                             const float* __restrict__ shift, float* __restrict__ hprev, int L,
@@ -71,8 +84,9 @@ __global__ void __launch_bounds__(256) prenorm_shift_kernel(const float* __restr
   if (t == 0) {  // this CTA alone touches hprev[b]: read above, replaced here
     const float* xl = xr + (size_t)(L - 1) * D;
     __syncthreads();  // every thread has read its hprev entries
-    row_rinv(xl, D, groups, eps, red, rl);
-    for (int i = threadIdx.x; i < D; i += blockDim.x) hprev[(size_t)b * D + i] = xl[i] * rl[i / gs] * w[i];
+    if (L > 1) row_rinv(xl, D, groups, eps, red, rl);
+    const float* rlast = L > 1 ? rl : rc;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) hprev[(size_t)b * D + i] = xl[i] * rlast[i / gs] * w[i];
   }
 }
 

@@ -99,6 +99,9 @@ class Debuzen(StackDecoder):
             raise ValueError("tensors=None needs random_seed")
         self.config = dict(config)
         shapes = {k: np.shape(v) for k, v in tensors.items()} if tensors is not None else None
+        lp = config.get("loop")
+        if tensors is not None and not (lp and int(lp.get("times", 0)) > 0) and "loop.in" in tensors:
+            tensors = {k: v for k, v in tensors.items() if k != "loop.in"}   # no pass ever starts: the entry projection is unused
         super().__init__(stack_config(config, shapes, max_seq_len=max_seq_len, max_batch_size=max_batch_size, dtype=dtype),
                          device=device, flags=flags)
         if tensors is not None:

@@ -301,14 +301,17 @@ class StackDecoder:
         """(S [heads, dim, vdim], conv tail [channels, taps - 1] or None) of a recurrent layer run's slot; for a
         latent-attention run S is its cache `[max_seq_len, kv_rank + rot_dim]`.  `layer` counts layer runs."""
         l = self.cfg.layers[self.run_layer(layer)]
+        if l.pair is not None and l.mixer == WINDOW:   # two mixers side by side: the recurrent one
+            l = l.pair
         if l.mixer == LATENT:
             S = np.empty((self.cfg.max_seq_len, l.kv_rank + l.rot_dim), dtype=np.float32)
             _cabi.check(self._lib.l3_read_state(self._h, layer, slot, _cabi.f32p(S), None), self._h)
             return S, None
         S = np.empty((l.heads, l.dim, l.vdim), dtype=np.float32)
         tail = None
-        if l.mixer == GATED_DELTA:
-            ch = 2 * (l.kv_heads or l.heads) * l.dim + l.heads * l.vdim
+        if l.mixer in (GATED_DELTA, SSD):
+            g = l.kv_heads or l.heads
+            ch = 2 * g * l.dim + l.heads * l.vdim
             tail = np.empty((ch, max(0, l.conv_taps - 1)), dtype=np.float32)
         _cabi.check(self._lib.l3_read_state(self._h, layer, slot, _cabi.f32p(S), _cabi.f32p(tail) if tail is not None and tail.size else None),
                     self._h)

@@ -305,6 +305,36 @@ def test_keys_far_away_through_the_recurrent_states():
     m.close()
 
 
+def test_states_after_a_prompt_and_after_a_slot_is_used_again():
+    """The recurrent state matrices and the convolutions' tails a prompt leaves, read back from the slot; then the same
+    slot runs another sequence in portions and must hold that sequence's state only."""
+    cfg = config([par(mlp=None), par2(mlp=None), gla(mlp=None)], width=48, vocab=50, groups=2, loop=(0, 2, 2))
+    m, o = build(cfg, seed=38)
+
+    def check(ids):
+        for run, (layer, _) in enumerate(o.runs):
+            S, tail = m.read_state(run)
+            st = o.state[run]
+            kind = cfg["layers"][layer]["type"]
+            want_S = st["S"] if kind == "gla" else st["right"]["S"]
+            assert np.allclose(S, want_S, rtol=1e-4, atol=1e-5), (run, kind)
+            if kind == "parallel":
+                r = st["right"]
+                assert np.allclose(tail, np.concatenate([r["tail_q"], r["tail_k"], r["tail_v"]]), rtol=1e-4, atol=1e-5), run
+            elif kind == "parallel_2":
+                assert np.allclose(tail, st["right"]["tail"], rtol=1e-4, atol=1e-5), run
+
+    ids = toks(21, 50, seed=39)
+    m.forward(ids[None], 0)
+    fresh(o).run(ids)
+    check(ids)
+    other = toks(9, 50, seed=40)
+    portions(m, other, [4, 1, 2, 1, 1])
+    fresh(o).run(other)
+    check(other)
+    m.close()
+
+
 ODD = {
     "one_head_one_group": [par(left=attn(heads=1, kv_heads=1, dim=8, vdim=8, size=1, keep_first=1, dims=0), heads=1, kv_heads=1, dim=8, vdim=8, conv=1),
                            par2(left=attn(heads=1, kv_heads=1, dim=16, vdim=8, size=3, dims=16), heads=1, groups=1, state=8, vdim=8, conv=1, norm_groups=1),
