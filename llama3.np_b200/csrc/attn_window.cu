@@ -114,7 +114,7 @@ __global__ void __launch_bounds__(256) win_attn_kernel(WinAttnArgs a) {
   const int g = blockIdx.y;
   const int b = blockIdx.z / a.nsplit, split = blockIdx.z - b * a.nsplit;
   const int nrows = a.L * rep;                     // rows of this (sequence, key head): row = t * rep + head in group
-  const int row0 = blockIdx.x * WA_ROWS;
+  const int row0 = (gridDim.x - 1 - blockIdx.x) * WA_ROWS;  // late tokens see the most keys: their tiles start first
   const int pos0 = *a.pos_ptr;
   const int t_lo = row0 / rep, t_hi = min(a.L - 1, (row0 + WA_ROWS - 1) / rep);
   const int p_lo = pos0 + t_lo, p_hi = pos0 + t_hi;

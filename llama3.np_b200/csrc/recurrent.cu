@@ -241,8 +241,8 @@ __global__ void __launch_bounds__(256) recur_pipe_kernel(RecurArgs a) {
     const float* vb = buf + NA * TCH * DKP;
     const float* bb = buf + TCH * (NA * DKP + CPB);
     int tok_first = 0;
-    if (MODE == 0 && TPC >= 4) {
-      // Fixed decay: nothing a token needs waits for a reduction, so four tokens' row partials are summed together -
+    if (MODE != 1 && TPC >= 4) {
+      // No delta step: nothing a token needs waits for a reduction, so four tokens' row partials are summed together -
       // a butterfly that halves the values a lane carries at the first two levels (5 shuffles for four tokens at
       // TPC = 16 instead of 16), after which lane s holds the complete sum of token s & 3.
       for (; tok_first + 4 <= n; tok_first += 4) {
@@ -255,12 +255,24 @@ __global__ void __launch_bounds__(256) recur_pipe_kernel(RecurArgs a) {
           const float qr[R] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
           const float vj = vb[(tok_first + u) * CPB + cl];
           float a0 = 0.f, a1 = 0.f;
+          if (MODE == 0) {
 #pragma unroll
-          for (int r = 0; r < 4; ++r) {
-            S[r] = fmaf(lam, S[r], kr[r] * vj);
-            S[r + 4] = fmaf(lam, S[r + 4], kr[r + 4] * vj);
-            a0 = fmaf(S[r], qr[r], a0);
-            a1 = fmaf(S[r + 4], qr[r + 4], a1);
+            for (int r = 0; r < 4; ++r) {
+              S[r] = fmaf(lam, S[r], kr[r] * vj);
+              S[r + 4] = fmaf(lam, S[r + 4], kr[r + 4] * vj);
+              a0 = fmaf(S[r], qr[r], a0);
+              a1 = fmaf(S[r + 4], qr[r + 4], a1);
+            }
+          } else {  // a decay per token and key channel
+            const float4 ga = g4[o4], gb = g4[o4 + TPC];
+            const float gr[R] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+              S[r] = fmaf(gr[r], S[r], kr[r] * vj);
+              S[r + 4] = fmaf(gr[r + 4], S[r + 4], kr[r + 4] * vj);
+              a0 = fmaf(S[r], qr[r], a0);
+              a1 = fmaf(S[r + 4], qr[r + 4], a1);
+            }
           }
           part[u] = a0 + a1;
         }
