@@ -445,6 +445,40 @@ def test_trace_runner_replays_a_trace(tmp_path):
         assert err(got, e) < FP32_BAR, i
 
 
+def test_generate_command_prints_the_loop_s_tokens(tmp_path):
+    import os
+    import subprocess
+    import sys
+    from conftest import ROOT
+    from llama3_np_b200.models import load_model
+    cfg = config([gla(), par2(), par()], width=48, vocab=47, groups=2, loop=(1, 3, 2))
+    _write_folder(tmp_path, cfg, random_tensors(cfg, 41))
+    prompts = np.stack([toks(7, 47, seed=s) for s in (42, 43)])
+    (tmp_path / "prompts.txt").write_text("\n".join(" ".join(str(int(x)) for x in p) for p in prompts) + "\n")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "generate"), "--model", str(tmp_path), "--dtype", "float32",
+                        "--batch-file", str(tmp_path / "prompts.txt"), "--new", "12"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    printed = np.array([[int(x) for x in line.split()] for line in r.stdout.strip().splitlines()[-2:]])
+    m = load_model(str(tmp_path), dtype="float32", max_seq_len=19, max_batch_size=2)
+    assert np.array_equal(printed, m.generate_all(prompts, 12))
+    m.close()
+
+
+def test_wide_windows_and_many_kept_tokens_over_several_key_tiles():
+    """Windows of 150 and 70 keys with 9 kept tokens over a prompt of 400: a query's keys span several 64-key tiles, the
+    kept tokens sit in a tile of their own ahead of the window, and short portions split the tiles over CTAs."""
+    a1 = attn(heads=4, kv_heads=2, dim=32, vdim=16, size=150, keep_first=9, dims=16, scale=0.2)
+    a2 = attn(heads=2, kv_heads=2, dim=16, vdim=48, size=70, dims=8, scale=0.3)
+    cfg = config([par(left=a1, mlp=None), par2(left=a2, mlp=None)], width=64, vocab=90, groups=2)
+    m, o = build(cfg, seed=44, max_seq_len=420)
+    ids = toks(400, 90, seed=45)
+    want = o.run(ids)
+    assert err(m.forward_rows(ids[None], 0, list(range(400))), want) < FP32_BAR
+    got = portions(m, ids, [130, 2, 64, 3, 100, 8, 1, 1, 50, 5, 1])
+    assert err(got, want) < FP32_BAR
+    m.close()
+
+
 def test_random_configurations():
     """Sizes, layer order, windows, kept tokens and loops drawn at random; whole prompts, portions, decoded tokens."""
     rng = np.random.default_rng(37)
