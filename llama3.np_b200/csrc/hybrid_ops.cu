@@ -30,7 +30,11 @@ __global__ void __launch_bounds__(256) ssd_prep_kernel(SsdPrepArgs a) {
   for (int h = threadIdx.x; h < a.H; h += blockDim.x) {
     const float dt = softplus_f(row[a.dt_off + h] + a.dt_bias[h]);
     sdt[h] = dt;
-    if (blockIdx.y == 0) a.decay_out[(size_t)r * a.H + h] = expf(-expf(a.A_log[h]) * dt);
+    if (blockIdx.y == 0) {
+      const float ld = -expf(a.A_log[h]) * dt;
+      a.decay_out[(size_t)r * a.H + h] = expf(ld);
+      if (a.logdecay_out) a.logdecay_out[(size_t)r * a.H + h] = ld;
+    }
   }
   __syncthreads();
   float* tail = a.conv_tail + (size_t)b * C * T1;

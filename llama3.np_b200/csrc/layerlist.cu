@@ -849,7 +849,7 @@ int ll_finalize(L3Model* m) {
         win_part = std::max(win_part, win_attn_part_floats(m->maxB * 8, H, DV, 32));
       } else if (s.mixer == L3_MIX_SSD) {
         max_rq = std::max(max_rq, G * DK); max_rk = std::max(max_rk, G * DK); max_rv = std::max(max_rv, H * DV);
-        max_rg = std::max(max_rg, H); max_xs = std::max(max_xs, H * DV);
+        max_rg = std::max(max_rg, 2 * H); max_xs = std::max(max_xs, H * DV);  // decays and their logarithms
       } else if (s.mixer == L3_MIX_GLA) {
         max_rq = std::max(max_rq, H * DK); max_rg = std::max(max_rg, H * DK); max_aux = std::max(max_aux, H * DK);
       }
@@ -938,9 +938,13 @@ int ll_finalize(L3Model* m) {
     CK(m, cudaMalloc((void**)&ll->moe_dense, ct * max_exp * 4));
     CK(m, cudaMalloc((void**)&ll->moe_idw, ct * 4));
   }
-  for (const LLLayer& L : ll->layers)
-    if (L.spec.mixer == L3_MIX_DECAY_LINEAR && recur_chunk_shape(L.spec.dim, L.spec.vdim) && ct >= 128)
-      ll->chunk_ws_floats = std::max(ll->chunk_ws_floats, (ct / 64 + m->maxB) * (size_t)L.spec.heads * L.spec.dim * L.spec.vdim);
+  for (const LLLayer& L0 : ll->layers)
+    for (const LLLayer* U = &L0; U; U = U->pair) {
+      const L3LayerSpec& s = U->spec;
+      const bool chunked = s.mixer == L3_MIX_DECAY_LINEAR || (units && s.mixer == L3_MIX_SSD);
+      if (chunked && recur_chunk_shape(s.dim, s.vdim) && ct >= 128)
+        ll->chunk_ws_floats = std::max(ll->chunk_ws_floats, (ct / 64 + m->maxB) * ((size_t)s.heads * s.dim * s.vdim + s.heads));
+    }
   if (ll->chunk_ws_floats) CK(m, cudaMalloc((void**)&ll->chunk_ws, ll->chunk_ws_floats * 4));
   // tensor cores: bf16 mode only.  fp32 mode is the exact mode of this family: every product is an fp32 FFMA chain
   // (the 3xTF32 scheme of the Llama path would need a (hi, lo) copy of the residual stream beside the stream itself).
@@ -1245,10 +1249,12 @@ static int ll_mix_unit(L3Model* m, LLLayer& Ly, LLState& St, const float* pin, i
     pa.proj = pin; pa.ld = ld; pa.xbc_off = Ly.off_q; pa.dt_off = Ly.off_b; pa.conv_w = Ly.conv_w; pa.conv_b = Ly.conv_b;
     pa.conv_tail = St.conv_tail; pa.A_log = Ly.A_log; pa.dt_bias = Ly.dt_bias;
     pa.x_out = ll->xs; pa.v_out = ll->rv; pa.k_out = ll->rk; pa.q_out = m->q; pa.decay_out = ll->rg;
+    pa.logdecay_out = ll->rg + (size_t)ntok * H;
     pa.L = L; pa.H = H; pa.G = G; pa.N = DK; pa.DV = DV; pa.taps = s.conv_taps; pa.update_tail = L == 1;
     LAUNCH(m, launch_ssd_prep(pa, ntok, m->stream));
     if (s.conv_taps > 1 && L > 1) LAUNCH(m, launch_conv_tail(St.conv_tail, pin + Ly.off_q, ld, B, L, O + 2 * gn, s.conv_taps - 1, m->stream));
     ra.mode = 2; ra.q = m->q; ra.k = ll->rk; ra.v = ll->rv; ra.ld_q = ra.ld_k = gn; ra.ld_v = O; ra.g = ll->rg; ra.g_head = 1; ra.rep = H / G;
+    ra.log_g = pa.logdecay_out; ra.ws = ll->chunk_ws; ra.ws_floats = ll->chunk_ws_floats;  // prompts: chunk-parallel where the shape allows
     LAUNCH(m, launch_recur(ra, m->stream));
     mo.skip_d = Ly.skip_d; mo.skip_x = ll->xs; mo.gate = pin + Ly.off_g; mo.ld_gate = ld; mo.gate_act = 1; mo.pre_gate = 1;
     mo.w = Ly.mix_norm; mo.wlen = O; mo.group = O / s.out_norm_groups;

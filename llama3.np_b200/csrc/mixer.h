@@ -64,6 +64,8 @@ struct RecurArgs {
   const float* head_decay;  // mode 0: [H]
   const float* g;         // mode 1, 2: [B * L, H * DK]; with g_head [B * L, H], one decay for all key channels of a head
   int g_head;
+  const float* log_g;     // mode 2 with g_head, may be null: [B * L, H] the decays' natural logarithms (finite); with it and
+                          // `ws`, prompts of the common shapes run in the chunk-parallel form
   const float* beta;      // mode 1: [B * L, H]
   float* state;           // [maxB, H, DK, DV]
   float* out;             // [B * L, H * DV]
@@ -290,6 +292,7 @@ struct SsdPrepArgs {
   float* v_out;           // [rows, H * DV] dt * x
   float *k_out, *q_out;   // [rows, G * N] B and C
   float* decay_out;       // [rows, H] exp(-exp(A_log) dt)
+  float* logdecay_out;    // [rows, H] -exp(A_log) dt (may be null)
   int L, H, G, N, DV, taps;
   int update_tail;        // L == 1 only: the kernel also moves conv_tail on by this token (no launch_conv_tail afterwards)
 };

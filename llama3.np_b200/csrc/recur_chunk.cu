@@ -1,6 +1,11 @@
-// Chunk-parallel form of the fixed-decay linear-attention recurrence (RecurArgs mode 0) for prompts.
+// Chunk-parallel form of the linear-attention recurrences whose decay is ONE number per head - fixed (RecurArgs mode 0)
+// or a new one for every token (mode 2 with g_head: the state-space mixer) - for prompts.
 //
 //   S_t = lam S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t
+//
+// (written below for a fixed lam; with a decay a_t per token every power lam^(i-j) becomes the product a_(j+1) .. a_i,
+// formed as exp(c_i - c_j) from the running sums c of the decays' logarithms inside the chunk, so that no product of
+// many small numbers is ever divided by another one.)
 //
 // Inside a chunk of CH tokens that starts from the state P, token i (0-based) reads
 //   o_i = lam^(i+1) P^T q_i + sum_{j <= i} lam^(i-j) (q_i . k_j) v_j
@@ -53,6 +58,28 @@ __device__ __forceinline__ void fill_powers(float* pw, float lam) {
   for (int p = threadIdx.x; p <= CH; p += blockDim.x) pw[p] = (float)pow((double)lam, (double)p);
 }
 
+// cl[j] = sum over t <= j of the chunk's log decays (tokens >= n add nothing): warp 0 scans, 32 tokens at a time
+__device__ __forceinline__ void fill_cumlog(float* cl, const float* __restrict__ lg, size_t stride, int n) {
+  if (threadIdx.x >= 32) return;
+  const int lane = threadIdx.x;
+  float carry = 0.f;
+  for (int j0 = 0; j0 < CH; j0 += 32) {
+    const int j = j0 + lane;
+    float v = j < n ? lg[(size_t)j * stride] : 0.f;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float t = __shfl_up_sync(L3_FULL, v, o);
+      if (lane >= o) v += t;
+    }
+    v += carry;
+    cl[j] = v;
+    carry = __shfl_sync(L3_FULL, v, 31);
+  }
+}
+
+// where the chunks' total decays live inside the workspace: behind the chunk states
+__device__ __forceinline__ float* chunk_decays(const RecurArgs& a, int NC) { return a.ws + (size_t)a.B * a.H * NC * a.DK * a.DV; }
+
 // rows [n, CH) of a natural [token][cols] tile and tokens >= n of the operands are zero: they add nothing
 __device__ __forceinline__ void load_natural(float* dst, int ld_dst, const float* src, size_t ld_src, int n, int cols, int act_in,
                                              const float* row_scale) {
@@ -89,6 +116,7 @@ __device__ __forceinline__ void load_transposed(float* dst, const float* src, si
 }
 
 // ---------------------------------------------------------------------------- 1. what a chunk adds to the state
+template <bool DEC>
 __global__ void __launch_bounds__(256) lin_chunk_state_kernel(RecurArgs a, int NC) {
   extern __shared__ __align__(16) float sm[];
   float* pw = sm;                 // [CH + 1] + scale per token [CH]
@@ -99,11 +127,13 @@ __global__ void __launch_bounds__(256) lin_chunk_state_kernel(RecurArgs a, int N
   pdl_wait();
   const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z, tid = threadIdx.x;
   const int n = min(CH, a.L - c * CH);
-  fill_powers(pw, a.head_decay[h]);
-  __syncthreads();
-  for (int j = tid; j < CH; j += blockDim.x) sc[j] = j < n ? pw[n - 1 - j] : 0.f;
-  __syncthreads();
   const size_t row0 = (size_t)b * a.L + (size_t)c * CH;
+  if (DEC) fill_cumlog(pw, a.log_g + row0 * a.H + h, a.H, n);
+  else fill_powers(pw, a.head_decay[h]);
+  __syncthreads();
+  for (int j = tid; j < CH; j += blockDim.x) sc[j] = j < n ? (DEC ? expf(pw[n - 1] - pw[j]) : pw[n - 1 - j]) : 0.f;
+  if (DEC && tid == 0) chunk_decays(a, NC)[((size_t)b * a.H + h) * NC + c] = expf(pw[n - 1]);
+  __syncthreads();
   load_natural(Ks, a.DK, a.k + row0 * a.ld_k + (size_t)(h / a.rep) * a.DK, a.ld_k, n, a.DK, a.act_in, sc);
   load_natural(Vs, a.DV, a.v + row0 * a.ld_v + (size_t)h * a.DV, a.ld_v, n, a.DV, a.act_in, nullptr);
   __syncthreads();
@@ -122,6 +152,7 @@ __global__ void __launch_bounds__(256) lin_chunk_state_kernel(RecurArgs a, int N
 }
 
 // ---------------------------------------------------------------------------- 2. the states between the chunks
+template <bool DEC>
 __global__ void __launch_bounds__(256) lin_chunk_scan_kernel(RecurArgs a, int NC) {
   pdl_launch();
   pdl_wait();
@@ -129,9 +160,10 @@ __global__ void __launch_bounds__(256) lin_chunk_scan_kernel(RecurArgs a, int NC
   const size_t n4 = (size_t)a.DK * a.DV / 4;
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n4) return;
-  const float lam = a.head_decay[h];
-  const float full = (float)pow((double)lam, (double)CH);
-  const float last = (float)pow((double)lam, (double)(a.L - (NC - 1) * CH));
+  const float lam = DEC ? 0.f : a.head_decay[h];
+  const float full = DEC ? 0.f : (float)pow((double)lam, (double)CH);
+  const float last = DEC ? 0.f : (float)pow((double)lam, (double)(a.L - (NC - 1) * CH));
+  const float* cdec = DEC ? chunk_decays(a, NC) + ((size_t)b * a.H + h) * NC : nullptr;
   float4* st = reinterpret_cast<float4*>(a.state + ((size_t)b * a.H + h) * a.DK * a.DV) + i;
   float4* W = reinterpret_cast<float4*>(a.ws + ((size_t)b * a.H + h) * NC * a.DK * a.DV) + i;
   float4 S = *st;
@@ -148,7 +180,7 @@ __global__ void __launch_bounds__(256) lin_chunk_scan_kernel(RecurArgs a, int NC
         const float4 cur = d[u];
         if (c + AHEAD < NC) d[u] = W[(size_t)(c + AHEAD) * n4];
         W[(size_t)c * n4] = S;
-        const float f = c == NC - 1 ? last : full;
+        const float f = DEC ? cdec[c] : c == NC - 1 ? last : full;
         S.x = f * S.x + cur.x; S.y = f * S.y + cur.y; S.z = f * S.z + cur.z; S.w = f * S.w + cur.w;
       }
     }
@@ -157,6 +189,7 @@ __global__ void __launch_bounds__(256) lin_chunk_scan_kernel(RecurArgs a, int NC
 }
 
 // ---------------------------------------------------------------------------- 3. the outputs of a chunk
+template <bool DEC>
 __global__ void __launch_bounds__(256) lin_chunk_out_kernel(RecurArgs a, int NC) {
   extern __shared__ __align__(16) float sm[];
   float* pw = sm;                            // [CH + 1]
@@ -170,7 +203,8 @@ __global__ void __launch_bounds__(256) lin_chunk_out_kernel(RecurArgs a, int NC)
   const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z, tid = threadIdx.x;
   const int n = min(CH, a.L - c * CH);
   const size_t row0 = (size_t)b * a.L + (size_t)c * CH;
-  fill_powers(pw, a.head_decay[h]);
+  if (DEC) fill_cumlog(pw, a.log_g + row0 * a.H + h, a.H, n);
+  else fill_powers(pw, a.head_decay[h]);
   load_transposed(Qt, a.q + row0 * a.ld_q + (size_t)(h / a.rep) * a.DK, a.ld_q, n, a.DK, a.act_in);
   load_transposed(Kt, a.k + row0 * a.ld_k + (size_t)(h / a.rep) * a.DK, a.ld_k, n, a.DK, a.act_in);
   __syncthreads();
@@ -187,7 +221,7 @@ __global__ void __launch_bounds__(256) lin_chunk_out_kernel(RecurArgs a, int NC)
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
         const int i = ty * 4 + r;
-        op[r] = j <= i ? acc[r][cc] * pw[i - j] : 0.f;
+        op[r] = j <= i ? acc[r][cc] * (DEC ? expf(pw[i] - pw[j]) : pw[i - j]) : 0.f;
       }
       *reinterpret_cast<float4*>(At + (size_t)j * LDT + ty * 4) = o;
     }
@@ -207,7 +241,7 @@ __global__ void __launch_bounds__(256) lin_chunk_out_kernel(RecurArgs a, int NC)
     mm44(Qt + ty * 4, LDT, Ps + tx * 4, 64, a.DK, acc);
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-      const float f = pw[ty * 4 + r + 1];
+      const float f = DEC ? expf(pw[ty * 4 + r]) : pw[ty * 4 + r + 1];
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc) acc[r][cc] *= f;
     }
@@ -227,13 +261,15 @@ bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 }  // namespace
 
 size_t recur_chunk_ws_floats(int B, int L, int H, int DK, int DV) {
-  return (size_t)B * H * ((L + CH - 1) / CH) * DK * DV;
+  const size_t NC = (L + CH - 1) / CH;
+  return (size_t)B * H * NC * DK * DV + (size_t)B * H * NC;  // chunk states, then the chunks' total decays
 }
 
 bool recur_chunk_shape(int DK, int DV) { return (DK == 64 || DK == 128) && DV % 64 == 0 && DV >= 64 && DV <= 512; }
 
 bool recur_chunk_supported(const RecurArgs& a) {
-  if (a.mode != 0 || !a.ws || a.L < 2 * CH) return false;
+  const bool per_token = a.mode == 2 && a.g_head && a.log_g;  // one decay per head and token
+  if ((a.mode != 0 && !per_token) || !a.ws || a.L < 2 * CH) return false;
   if (!recur_chunk_shape(a.DK, a.DV)) return false;
   if (a.ld_q % 4 || a.ld_k % 4 || a.ld_v % 4 || (a.H * a.DV) % 4) return false;
   if (!aligned16(a.q) || !aligned16(a.k) || !aligned16(a.v) || !aligned16(a.out) || !aligned16(a.ws) || !aligned16(a.state)) return false;
@@ -247,10 +283,17 @@ cudaError_t launch_recur_chunk(const RecurArgs& a, cudaStream_t s) {
   const size_t sm1 = (size_t)(CH + 4 + CH + CH * a.DK + CH * a.DV) * sizeof(float);
   const size_t sm3 = (size_t)(CH + 4 + 2 * a.DK * LDT + CH * LDT + CH * 64) * sizeof(float);
   cudaError_t e;
-  if ((e = cudaFuncSetAttribute(lin_chunk_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm1)) != cudaSuccess) return e;
-  if ((e = cudaFuncSetAttribute(lin_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm3)) != cudaSuccess) return e;
-  if ((e = launch_k(lin_chunk_state_kernel, grid, dim3(256), sm1, s, a, NC)) != cudaSuccess) return e;
   const int n4 = a.DK * a.DV / 4;
-  if ((e = launch_k(lin_chunk_scan_kernel, dim3((n4 + 255) / 256, a.H, a.B), dim3(256), 0, s, a, NC)) != cudaSuccess) return e;
-  return launch_k(lin_chunk_out_kernel, grid, dim3(256), sm3, s, a, NC);
+  if (a.mode == 2) {
+    if ((e = cudaFuncSetAttribute(lin_chunk_state_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm1)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(lin_chunk_out_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm3)) != cudaSuccess) return e;
+    if ((e = launch_k(lin_chunk_state_kernel<true>, grid, dim3(256), sm1, s, a, NC)) != cudaSuccess) return e;
+    if ((e = launch_k(lin_chunk_scan_kernel<true>, dim3((n4 + 255) / 256, a.H, a.B), dim3(256), 0, s, a, NC)) != cudaSuccess) return e;
+    return launch_k(lin_chunk_out_kernel<true>, grid, dim3(256), sm3, s, a, NC);
+  }
+  if ((e = cudaFuncSetAttribute(lin_chunk_state_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm1)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(lin_chunk_out_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm3)) != cudaSuccess) return e;
+  if ((e = launch_k(lin_chunk_state_kernel<false>, grid, dim3(256), sm1, s, a, NC)) != cudaSuccess) return e;
+  if ((e = launch_k(lin_chunk_scan_kernel<false>, dim3((n4 + 255) / 256, a.H, a.B), dim3(256), 0, s, a, NC)) != cudaSuccess) return e;
+  return launch_k(lin_chunk_out_kernel<false>, grid, dim3(256), sm3, s, a, NC);
 }

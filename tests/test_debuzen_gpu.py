@@ -479,6 +479,28 @@ def test_wide_windows_and_many_kept_tokens_over_several_key_tiles():
     m.close()
 
 
+@pytest.mark.parametrize("fast_decay", [False, True])
+def test_long_prompts_of_state_space_layers_run_chunk_parallel(fast_decay):
+    """States of 64 x 64 and prompts of 128 tokens and more take the chunk-parallel form of the recurrence (sums in another
+    order than the token-by-token chain): both must agree with the oracle and with each other, also where the decays are so
+    small that a chunk's product of them underflows."""
+    a2 = attn(heads=2, kv_heads=1, dim=16, vdim=16, size=20, dims=8)
+    cfg = config([par2(left=a2, heads=4, groups=2, state=64, vdim=64, conv=4, norm_groups=2, mlp=None), gla(mlp=None)], width=64, vocab=80, groups=2)
+    t = random_tensors(cfg, 46)
+    if fast_decay:
+        t["l0.mix.right.dt_bias"] = np.full(4, 4.0, np.float32)
+        t["l0.mix.right.A_log"] = np.array([1.0, 0.5, 2.0, -1.0], np.float32)
+    m, o = build(cfg, tensors=t, max_seq_len=400)
+    ids = toks(390, 80, seed=47)
+    want = o.run(ids)
+    whole = m.forward_rows(ids[None], 0, list(range(390)))
+    assert err(whole, want) < FP32_BAR
+    mixed = portions(m, ids, [130, 3, 192, 1, 1, 40, 23])
+    assert err(mixed, want) < FP32_BAR
+    assert err(mixed, whole) < 2e-5
+    m.close()
+
+
 def test_random_configurations():
     """Sizes, layer order, windows, kept tokens and loops drawn at random; whole prompts, portions, decoded tokens."""
     rng = np.random.default_rng(37)
